@@ -1,0 +1,137 @@
+/*
+ * C ABI of the B200 (sm_100a) NVFP4 hot-path library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (a cudaStream_t passed as void*; NULL selects the legacy default stream), is
+ * asynchronous on that stream, allocates no output memory and returns an int
+ * status (B2_OK on success).  No exception crosses this boundary; a human
+ * readable reason for the last failure of the calling thread is returned by
+ * b2_last_error().
+ *
+ * Each declaration names the reference interface it stands in for, by the
+ * path of the file inside the mlc-ai/TIRx-kernels project.
+ */
+#ifndef B200_NVFP4_H_
+#define B200_NVFP4_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+#define B2_OK 0
+#define B2_ERR_INVALID_ARGUMENT 1 /* shape / alignment / null pointer; nothing was launched   */
+#define B2_ERR_CUDA 2             /* a CUDA runtime or driver call failed                      */
+#define B2_ERR_DEVICE_TIMEOUT 3   /* a bounded device-side wait expired (read by *_status())   */
+#define B2_ERR_UNSUPPORTED 4      /* valid in the reference, not built here yet                */
+
+/* ---- enums (ints on the wire) ------------------------------------------- */
+#define B2_DTYPE_F16 0
+#define B2_DTYPE_BF16 1
+
+#define B2_SF_LINEAR 0 /* uint8[m, k/16] row-major                                   */
+#define B2_SF_128x4 1  /* 128-row x 4-column tiles of 512 B, the tcgen05 / cuBLASLt layout */
+#define B2_SF_8x4 2    /* 8-row x 4-column tiles of 32 B                            */
+
+#define B2_SCALE_E4M3 0
+#define B2_SCALE_UE8M0 1
+
+/* op codes of b2_mufu_probe */
+#define B2_MUFU_RCP_FTZ 0   /* rcp.approx.ftz.f32   */
+#define B2_MUFU_RSQRT_FTZ 1 /* rsqrt.approx.ftz.f32 */
+#define B2_MUFU_LG2 2       /* lg2.approx.f32       */
+#define B2_MUFU_EX2 3       /* ex2.approx.f32       */
+#define B2_MUFU_EX2_FTZ 4   /* ex2.approx.ftz.f32   */
+
+/* Reason for the most recent non-zero status returned to this thread. */
+const char* b2_last_error(void);
+
+/* Library ABI version (bumped when a signature changes). */
+int b2_abi_version(void);
+
+/*
+ * NVFP4 block quantizer.
+ *
+ * Replaces the executables returned by get_kernel() in
+ * tirx_kernels/flashinfer/quantization/nvfp4_quantize.py:191-377
+ * (nvfp4_quantize_linear :214-221, nvfp4_quantize_swizzled :259-266), launched
+ * by _run_launch :441-445.
+ *
+ *   in       [m, k] (or [m, 2k] = [gate | up] when fuse_silu) fp16/bf16, row-major
+ *   out      uint8 [m, k/2]: element 2j in the low nibble, 2j+1 in the high nibble
+ *   sf       uint8 scale factors, one E4M3 byte per 16 elements, in sf_layout;
+ *            swizzled layouts are zero-filled in their padding rows and columns
+ *   gs_dev   device pointer to the fp32 global (encode) scale
+ * Requirements: k > 0, k % 16 == 0, m >= 1, `in` 32-byte aligned, `out` 8-byte aligned.
+ */
+int b2_nvfp4_quantize(const void* in, void* out, void* sf, const float* gs_dev, int m, int k,
+                      int in_dtype, int sf_layout, int fuse_silu, int enable_pdl, void* stream);
+
+/* Number of bytes of the scale-factor buffer for (m, k, sf_layout); mirrors
+ * _sf_numel, tirx_kernels/flashinfer/quantization/nvfp4_quantize.py:126-129. */
+int64_t b2_nvfp4_sf_bytes(int m, int k, int sf_layout);
+
+/*
+ * RMSNorm fused with FP4 block quantization.
+ *
+ * Replaces the executable returned by get_kernel() in
+ * tirx_kernels/flashinfer/norm/rmsnorm_fp4quant.py:707-1033 (entry signature
+ * :983-991, launched by _launch_tirx :1156-1165).
+ *
+ *   x        [M, H] fp16/bf16 row-major;  w  [H] same dtype
+ *   y        uint8 [M, H/2] packed E2M1
+ *   sf       block_size 16: E4M3 bytes; block_size 32: E4M3 or UE8M0 bytes; linear
+ *            [M, H/block_size] or 128x4-swizzled (padding positions are left untouched)
+ *   gs_dev   fp32 global scale (read only when the scale format in effect is E4M3)
+ * Requirements: H >= 64, H % block_size == 0, M >= 1.
+ */
+int b2_rmsnorm_fp4quant(const void* x, const void* w, void* y, void* sf, const float* gs_dev,
+                        int M, int H, float eps, int in_dtype, int block_size, int scale_format,
+                        int swizzled, int enable_pdl, void* stream);
+
+/*
+ * Dense block-scaled NVFP4 GEMM:  D[M,N] (bf16) = alpha * A[M,K] * B[N,K]^T.
+ *
+ * Replaces _Runner.__call__ in tirx_kernels/basic/nvfp4_gemm.py:985-997 (kernel
+ * :374-857, tensor maps :941-982).
+ *
+ *   A, B       packed E2M1, K-major: uint8 [M, K/2] and uint8 [N, K/2]
+ *   SFA, SFB   E4M3 block scales (one per 16 along K) in the 128x4-swizzled layout,
+ *              ceil(M/128)*128 x K/16 and ceil(N/128)*128 x K/16 bytes
+ *   alpha_dev  device fp32 scalar (1 / (encode scale of A * encode scale of B))
+ * Requirements: K % 256 == 0, N % 128 == 0, M >= 1, all pointers 16-byte aligned.
+ * Tensor maps are cached per (pointers, shape) inside the library.
+ */
+int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, const void* SFB,
+                  const float* alpha_dev, void* D, int M, int N, int K, void* stream);
+
+/* Reads (and clears) the device status word written by bounded waits inside
+ * b2_nvfp4_gemm on the current device; synchronises `stream` first.
+ * Returns B2_OK, or B2_ERR_DEVICE_TIMEOUT with the detail in b2_last_error(). */
+int b2_nvfp4_gemm_status(void* stream);
+
+/*
+ * cuBLASLt NVFP4 matmul, the library peer the reference times beside its own
+ * kernel: nvfp4_cublaslt in tirx_kernels/basic/nvfp4_gemm.py:196-239.
+ * Lives in a separate shared object (libb200nvfp4_cublaslt.so) so the product
+ * library carries no cuBLAS dependency.  `alpha` is a host scalar, as in the reference.
+ */
+int b2_nvfp4_gemm_cublaslt(const void* A, const void* B, const void* SFA, const void* SFB,
+                           float alpha, void* D, int M, int N, int K, void* stream);
+
+/*
+ * Evaluates one hardware-approximate (MUFU) instruction elementwise:
+ * out[i] = op(in[i]).  Test infrastructure for the CPU oracle: these
+ * instructions (used by fp_quant.py rcp_approx_ftz :277-281 and
+ * rmsnorm_fp4quant.py _rsqrt_approx_ftz :78-79, _cvt_f32_to_ue8m0 :155-171,
+ * _ue8m0_to_output_scale :174-185) are not specified bit-for-bit, so the oracle
+ * takes their values from the hardware and computes everything else itself.
+ */
+int b2_mufu_probe(int op, const float* in_dev, float* out_dev, int n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_NVFP4_H_ */

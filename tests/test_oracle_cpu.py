@@ -1,0 +1,133 @@
+"""CPU checks of the oracle itself: format conversions, layouts, the two restatements against
+each other, and the self-contained checks the reference carries for this path."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle
+from oracle import nvfp4_oracle as o
+
+
+def _bits(t):
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def test_e4m3_encode_matches_torch_cast_and_saturates():
+    rng = np.random.default_rng(0)
+    v = np.concatenate([np.linspace(0, 448, 100001, dtype=np.float32),
+                        rng.uniform(0, 448, 100000).astype(np.float32),
+                        rng.uniform(0, 2.0**-5, 20000).astype(np.float32), o.E4M3_VALUES[:127]])
+    expected = torch.from_numpy(v).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(o.e4m3_encode(v), expected)
+    # torch's cast yields NaN above 464; the PTX conversion saturates to 448 (0x7E)
+    assert list(o.e4m3_encode(np.array([449.0, 465.0, 1e9, np.inf], dtype=np.float32))) == [0x7E] * 4
+    assert o.e4m3_encode(np.array([np.nan], dtype=np.float32))[0] == 0x7F
+
+
+def test_e4m3_and_e2m1_round_trip_every_code():
+    assert np.array_equal(o.e4m3_encode(o.E4M3_VALUES[:127]), np.arange(127))
+    assert np.array_equal(o.e4m3_encode(o.E4M3_VALUES[128:255]), np.arange(128, 255))
+    assert np.array_equal(o.e2m1_encode(o.E2M1_VALUES), np.arange(16))
+
+
+def test_e2m1_ties_go_to_even_and_saturate():
+    ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.5, 1e9], dtype=np.float32)
+    assert [o.E2M1_VALUES[c] for c in o.e2m1_encode(ties)] == [0, 1, 1, 2, 2, 4, 4, 6, 6]
+    assert list(o.e2m1_encode(-ties)) == [c | 8 for c in o.e2m1_encode(ties)]
+    assert o.e2m1_encode(np.array([-0.0], dtype=np.float32))[0] == 0x8
+
+
+@pytest.mark.parametrize("layout", ["128x4", "8x4"])
+@pytest.mark.parametrize("m,cols", [(1, 1), (13, 65), (120, 64), (129, 5), (256, 516)])
+def test_swizzled_offsets_are_a_bijection_into_the_padded_buffer(layout, m, cols):
+    pad = o.padded_sf_cols(cols)
+    tile = 8 if layout == "8x4" else 128
+    rows_padded = -(-m // tile) * tile
+    off = o.sf_offsets(layout, np.arange(rows_padded)[:, None], np.arange(pad)[None, :], pad).reshape(-1)
+    assert np.array_equal(np.sort(off), np.arange(rows_padded * pad))
+    assert o.sf_buffer_size(m, cols, layout) == rows_padded * pad
+
+
+def test_bf16_and_f16_products_round_once():
+    rng = np.random.default_rng(1)
+    a = rng.integers(0, 1 << 16, 200000).astype(np.uint16)
+    b = rng.integers(0, 1 << 16, 200000).astype(np.uint16)
+    for dtype, tdt in ((o.BF16, torch.bfloat16), (o.F16, torch.float16)):
+        ta = torch.from_numpy(a.view(np.int16)).view(tdt)
+        tb = torch.from_numpy(b.view(np.int16)).view(tdt)
+        want = (ta.double() * tb.double()).to(tdt).float().numpy()
+        got = o.mul_16bit(a, b, dtype)
+        ok = np.isnan(want) | (want == got)
+        assert ok.all()
+
+
+@pytest.mark.parametrize("dtype,tdt", [(o.BF16, torch.bfloat16), (o.F16, torch.float16)])
+@pytest.mark.parametrize("m,k,layout", [(1, 16, "linear"), (13, 1040, "linear"), (120, 1024, "128x4"),
+                                        (128, 1040, "128x4"), (13, 1024, "8x4"), (64, 8208, "128x4")])
+def test_c_and_numpy_quantizers_agree(dtype, tdt, m, k, layout):
+    g = torch.Generator().manual_seed(7)
+    bits = _bits(torch.randn(m, k, generator=g).to(tdt))
+    a = o.nvfp4_quantize(bits, dtype, 0.83, layout)
+    b = c_oracle.nvfp4_quantize(bits, dtype, 0.83, layout)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+
+
+@pytest.mark.parametrize("dtype,tdt", [(o.BF16, torch.bfloat16), (o.F16, torch.float16)])
+@pytest.mark.parametrize("M,H,swizzled", [(17, 64, False), (129, 80, True), (3, 3072, False), (3, 3088, True),
+                                          (3, 6160, False), (5, 7168, True), (3, 16400, False), (2, 32768, False)])
+def test_c_and_numpy_rmsnorm_agree(dtype, tdt, M, H, swizzled):
+    g = torch.Generator().manual_seed(9)
+    x = _bits(torch.randn(M, H, generator=g).to(tdt))
+    w = _bits(torch.randn(H, generator=g).to(tdt))
+    a = o.rmsnorm_fp4quant(x, w, dtype, 21.0, 1e-6, swizzled=swizzled, sf_fill=0xA5)
+    b = c_oracle.rmsnorm_fp4quant(x, w, dtype, 21.0, 1e-6, swizzled=swizzled, sf_fill=0xA5)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1].reshape(-1), b[1].reshape(-1))
+
+
+def test_quantizer_output_decodes_close_to_the_input():
+    g = torch.Generator().manual_seed(42)
+    x = torch.randn(256, 2048, generator=g).to(torch.bfloat16)
+    gs = np.float32(2688.0 / x.float().abs().max().item())
+    packed, sf = o.nvfp4_quantize(_bits(x), o.BF16, gs, "128x4")
+    deq = o.dequantize_nvfp4(packed, sf, "128x4", gs)
+    ref = x.float().numpy()
+    assert np.linalg.norm(deq - ref) / np.linalg.norm(ref) < 0.12
+    assert np.array_equal(deq, c_oracle.dequantize_nvfp4(packed, sf, "128x4", gs))
+
+
+@pytest.mark.parametrize("block_size,scale_format", [(16, "e4m3"), (32, "ue8m0"), (32, "e4m3")])
+def test_rmsnorm_oracle_passes_the_reference_math_check(block_size, scale_format):
+    """rtol 0.5 / atol 2.0 against an fp32 RMSNorm: rmsnorm_fp4quant.py _assert_math :1334-1344."""
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(33, 4096, generator=g).to(torch.float16)
+    w = torch.randn(4096, generator=g).to(torch.float16)
+    gs = 3.25
+    packed, sf = o.rmsnorm_fp4quant(_bits(x), _bits(w), o.F16, gs, 1e-6, block_size, scale_format)
+    if block_size == 16 or scale_format == "e4m3":
+        deq = o.dequantize_nvfp4(packed, sf, "linear", gs, block_size)
+    else:
+        deq = o.dequantize_mxfp4(packed, sf, "linear", block_size)
+    ref = o.rmsnorm_reference_f32(_bits(x), _bits(w), o.F16, 1e-6)
+    assert np.isfinite(deq).all()
+    assert np.all(np.abs(deq - ref) <= 2.0 + 0.5 * np.abs(ref))
+
+
+def test_zero_global_scale_gives_signed_zero_values_and_zero_scales():
+    """rmsnorm_fp4quant.py :1325-1332."""
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(3, 4096, generator=g).to(torch.float16)
+    w = torch.randn(4096, generator=g).to(torch.float16)
+    packed, sf = o.rmsnorm_fp4quant(_bits(x), _bits(w), o.F16, 0.0, 1e-6)
+    assert not np.any(packed & 0x77) and not np.any(sf)
+
+
+def test_cluster_reduction_tree_is_restated():
+    cfg = o.source_config(65536)
+    assert (cfg["cluster_n"], cfg["tpr"], cfg["vec_blocks"]) == (2, 256, 16)
+    assert o.source_config(1048576)["cluster_n"] == 16
+    g = torch.Generator().manual_seed(5)
+    x = _bits(torch.randn(2, 65536, generator=g).to(torch.bfloat16))
+    s = o.rmsnorm_sum_of_squares(x, o.BF16)
+    ref = (o.bits_to_f32(x, o.BF16).astype(np.float64) ** 2).sum(-1)
+    assert np.allclose(s, ref, rtol=1e-6)

@@ -1,0 +1,300 @@
+// RMSNorm fused with FP4 block quantization for sm_100a.
+//
+// Bit parity with tirx_kernels/flashinfer/norm/rmsnorm_fp4quant.py requires the fp32
+// sum of squares to be accumulated in exactly the reference's order (kernel_body
+// :786-900): with tpr = threads_per_row(H) (:344-355), virtual thread t owns the
+// 8-element chunks t, t+tpr, t+2*tpr, ... of its row and adds their squares one by
+// one; partial sums are combined by an XOR butterfly inside the warp and, for rows
+// wider than a warp, by a second butterfly over the per-warp partials.  This kernel
+// keeps that tree and changes the data movement: the row is read from HBM exactly
+// once with 128-bit loads, parked in shared memory, and the quantization pass reads
+// it back from there; each thread quantizes 8 values (block amax by a 2- or 4-lane
+// shuffle) so packed output is written as fully coalesced 32-bit words.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace b2 {
+namespace {
+
+struct RmsParams {
+  const uint8_t* x;
+  const uint8_t* w;
+  uint8_t* y;
+  uint8_t* sf;
+  const float* gs;
+  int M;
+  int H;
+  int vb;            // chunks of 8 values per virtual thread
+  int block_size;    // 16 or 32
+  int use_e4m3;      // E4M3 scales under a global scale, else UE8M0
+  int swizzled;
+  int sf_cols;       // H / block_size
+  int sf_pad_cols;   // sf_cols rounded up to 4
+  int pow2;          // H is a power of two
+  float eps;
+  float inv_h;       // 1.0f / H (exact when pow2)
+  int enable_pdl;
+};
+
+// rmsnorm_fp4quant.py _cvt_f32_to_ue8m0 :155-171
+__device__ __forceinline__ uint32_t cvt_f32_to_ue8m0(float v) {
+  const bool is_zero = v <= 0.0f;
+  int r = __float2int_ru(lg2_approx(v)) + 127;
+  r = r < 0 ? 0 : r;
+  r = r > 255 ? 255 : r;
+  return is_zero ? 0u : static_cast<uint32_t>(r);
+}
+// rmsnorm_fp4quant.py _ue8m0_to_output_scale :174-185
+__device__ __forceinline__ float ue8m0_to_output_scale(uint32_t code) {
+  const float cand = ex2_approx(__int2float_rn(127 - static_cast<int>(code)));
+  return code == 0u ? 0.0f : cand;
+}
+
+template <typename Tag>
+__device__ __forceinline__ float sum_sq_8(float acc, const uint4& c) {
+  const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float lo = unpack_lo<Tag>(w[i]), hi = unpack_hi<Tag>(w[i]);
+    acc = add_f32(acc, mul_f32(lo, lo));
+    acc = add_f32(acc, mul_f32(hi, hi));
+  }
+  return acc;
+}
+
+template <typename Tag, int TPR>
+__global__ void __launch_bounds__(TPR == 256 ? 256 : 128)
+    rmsnorm_fp4quant_kernel(const __grid_constant__ RmsParams p) {
+  constexpr int kThreads = TPR == 256 ? 256 : 128;
+  constexpr int kRows = kThreads / TPR;
+  constexpr int kWarpsPerRow = TPR >= 32 ? TPR / 32 : 1;
+  extern __shared__ __align__(16) uint8_t smem[];
+  uint4* tile = reinterpret_cast<uint4*>(smem);  // [kRows][vb][TPR] chunks of 8 values
+  float* red = reinterpret_cast<float*>(smem + static_cast<size_t>(kRows) * p.vb * TPR * 16);
+
+  const int tid = threadIdx.x;
+  const int row_in_cta = tid / TPR;
+  const int t = tid % TPR;
+  const int row = blockIdx.x * kRows + row_in_cta;
+  const bool row_valid = row < p.M;
+  const int nchunks = p.H >> 3;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+
+  if (p.enable_pdl) pdl_wait();
+
+  const float rcp6 = rcp_approx_ftz(6.0f);
+  const uint4* xrow = reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(row) * p.H * 2);
+  uint4* my_tile = tile + static_cast<size_t>(row_in_cta) * p.vb * TPR + t;
+
+  // ---- pass 1: one HBM read of the row, squares accumulated in chunk order -------------
+  float sum = 0.0f;
+  for (int b0 = 0; b0 < p.vb; b0 += 4) {
+    uint4 c[4];
+    bool ok[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int chunk = t + (b0 + j) * TPR;
+      ok[j] = row_valid && (b0 + j) < p.vb && chunk < nchunks;
+      if (ok[j]) {
+        uint32_t r[4];
+        ld_stream_128(xrow + chunk, r);
+        c[j] = make_uint4(r[0], r[1], r[2], r[3]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (ok[j]) {
+        my_tile[(b0 + j) * TPR] = c[j];
+        sum = sum_sq_8<Tag>(sum, c[j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int x = 1; x < (TPR < 32 ? TPR : 32); x <<= 1) {
+    sum = add_f32(sum, __shfl_xor_sync(0xFFFFFFFFu, sum, x));
+  }
+  if constexpr (kWarpsPerRow > 1) {
+    const int row_warp = warp / kWarpsPerRow;
+    const int warp_in_row = warp % kWarpsPerRow;
+    if (lane == 0) red[row_warp + warp_in_row * kRows] = sum;
+    __syncthreads();
+    float part = lane < kWarpsPerRow ? red[row_warp + lane * kRows] : 0.0f;
+#pragma unroll
+    for (int x = 1; x < 32; x <<= 1) part = add_f32(part, __shfl_xor_sync(0xFFFFFFFFu, part, x));
+    sum = part;
+  }
+  const float shifted =
+      p.pow2 ? __fmaf_rn(sum, p.inv_h, p.eps) : add_f32(__fdiv_rn(sum, static_cast<float>(p.H)), p.eps);
+  const float rstd = rsqrt_approx_ftz(shifted);
+  const float gs = p.use_e4m3 ? *p.gs : 0.0f;
+
+  // ---- pass 2: scale, quantize and pack from the shared-memory copy ---------------------
+  const uint4* wrow = reinterpret_cast<const uint4*>(p.w);
+  const int group = p.block_size >> 3;  // lanes sharing one scale factor: 2 or 4
+  uint8_t* yrow = p.y + static_cast<int64_t>(row) * (p.H >> 1);
+  for (int b = 0; b < p.vb; ++b) {
+    const int chunk = t + b * TPR;
+    const bool ok = row_valid && chunk < nchunks;
+    uint32_t prod[4] = {0u, 0u, 0u, 0u};
+    if (ok) {
+      const uint4 xc = my_tile[b * TPR];
+      const uint4 wc = __ldg(wrow + chunk);
+      prod[0] = hmul2<Tag>(xc.x, wc.x);
+      prod[1] = hmul2<Tag>(xc.y, wc.y);
+      prod[2] = hmul2<Tag>(xc.z, wc.z);
+      prod[3] = hmul2<Tag>(xc.w, wc.w);
+    }
+    float amax = pair_max_to_f32<Tag>(absmax_4<Tag>(prod));
+    amax = max_f32(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    if (group == 4) amax = max_f32(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    if (!ok) continue;
+
+    const float max_abs = mul_f32(amax, rstd);
+    uint32_t code;
+    float out_scale;
+    if (p.use_e4m3) {
+      const float s = min_f32(mul_f32(mul_f32(gs, max_abs), rcp6), 448.0f);
+      code = cvt_f32_to_e4m3(s) & 0xFFu;
+      const float d = e4m3_to_f32(code);
+      const float r = rcp_approx_ftz(d);
+      out_scale = mul_f32(d == 0.0f ? 0.0f : r, gs);
+    } else {
+      code = cvt_f32_to_ue8m0(mul_f32(max_abs, rcp6));
+      out_scale = ue8m0_to_output_scale(code);
+    }
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = mul_f32(mul_f32(unpack_lo<Tag>(prod[i]), rstd), out_scale);
+      v[2 * i + 1] = mul_f32(mul_f32(unpack_hi<Tag>(prod[i]), rstd), out_scale);
+    }
+    *reinterpret_cast<uint32_t*>(yrow + chunk * 4) = cvt_e2m1x8(v);
+    if ((chunk & (group - 1)) == 0) {
+      const int sf_index = chunk / group;
+      const int64_t off = p.swizzled ? sf_offset_128x4(row, sf_index, p.sf_pad_cols)
+                                     : static_cast<int64_t>(row) * p.sf_cols + sf_index;
+      p.sf[off] = static_cast<uint8_t>(code);
+    }
+  }
+  if (p.enable_pdl) pdl_launch_dependents();
+}
+
+// rmsnorm_fp4quant.py _threads_per_row :344-355
+int threads_per_row(int h) {
+  if (h <= 64) return 8;
+  if (h <= 128) return 16;
+  if (h <= 3072) return 32;
+  if (h <= 6144) return 64;
+  if (h <= 16384) return 128;
+  return 256;
+}
+
+template <typename Tag, int TPR>
+int launch(const RmsParams& p, cudaStream_t stream) {
+  constexpr int kThreads = TPR == 256 ? 256 : 128;
+  constexpr int kRows = kThreads / TPR;
+  constexpr int kWarpsPerRow = TPR >= 32 ? TPR / 32 : 1;
+  auto kernel = rmsnorm_fp4quant_kernel<Tag, TPR>;
+  const size_t smem = static_cast<size_t>(kRows) * p.vb * TPR * 16 + kRows * kWarpsPerRow * 4;
+  if (smem > 48 * 1024) {
+    B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem)));
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((p.M + kRows - 1) / kRows);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (p.enable_pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p));
+  return B2_OK;
+}
+
+template <typename Tag>
+int dispatch_tpr(const RmsParams& p, int tpr, cudaStream_t stream) {
+  switch (tpr) {
+    case 8: return launch<Tag, 8>(p, stream);
+    case 16: return launch<Tag, 16>(p, stream);
+    case 32: return launch<Tag, 32>(p, stream);
+    case 64: return launch<Tag, 64>(p, stream);
+    case 128: return launch<Tag, 128>(p, stream);
+    default: return launch<Tag, 256>(p, stream);
+  }
+}
+
+}  // namespace
+}  // namespace b2
+
+extern "C" int b2_rmsnorm_fp4quant(const void* x, const void* w, void* y, void* sf,
+                                   const float* gs_dev, int M, int H, float eps, int in_dtype,
+                                   int block_size, int scale_format, int swizzled, int enable_pdl,
+                                   void* stream) {
+  using namespace b2;
+  if (in_dtype != B2_DTYPE_F16 && in_dtype != B2_DTYPE_BF16) {
+    set_error("b2_rmsnorm_fp4quant: unsupported input_dtype %d", in_dtype);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (block_size != 16 && block_size != 32) {
+    set_error("b2_rmsnorm_fp4quant: unsupported block_size=%d", block_size);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (H < 64 || H % block_size != 0) {
+    set_error("b2_rmsnorm_fp4quant: H=%d must be >=64 and divisible by block_size=%d", H, block_size);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (scale_format != B2_SCALE_E4M3 && scale_format != B2_SCALE_UE8M0) {
+    set_error("b2_rmsnorm_fp4quant: unsupported scale_format %d", scale_format);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (M <= 0) {
+    set_error("b2_rmsnorm_fp4quant: M must be positive, got %d", M);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  const bool use_e4m3 = block_size == 16 || scale_format == B2_SCALE_E4M3;
+  if (!x || !w || !y || !sf || (use_e4m3 && !gs_dev)) {
+    set_error("b2_rmsnorm_fp4quant: null pointer argument");
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
+      (reinterpret_cast<uintptr_t>(y) & 3)) {
+    set_error("b2_rmsnorm_fp4quant: x and w must be 16-byte aligned, y 4-byte aligned");
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  const int tpr = threads_per_row(H);
+  RmsParams p;
+  p.x = static_cast<const uint8_t*>(x);
+  p.w = static_cast<const uint8_t*>(w);
+  p.y = static_cast<uint8_t*>(y);
+  p.sf = static_cast<uint8_t*>(sf);
+  p.gs = gs_dev;
+  p.M = M;
+  p.H = H;
+  p.vb = std::max(1, ((H / 8) + tpr - 1) / tpr);
+  p.block_size = block_size;
+  p.use_e4m3 = use_e4m3 ? 1 : 0;
+  p.swizzled = swizzled ? 1 : 0;
+  p.sf_cols = H / block_size;
+  p.sf_pad_cols = (p.sf_cols + 3) / 4 * 4;
+  p.pow2 = (H & (H - 1)) == 0;
+  p.eps = eps;
+  p.inv_h = 1.0f / static_cast<float>(H);
+  p.enable_pdl = enable_pdl ? 1 : 0;
+  // Rows that the reference splits over a thread-block cluster (one CTA cannot hold
+  // the row in shared memory) use a different reduction tree; not built yet.
+  const size_t tile_bytes = static_cast<size_t>(p.vb) * tpr * 16 * ((tpr == 256 ? 256 : 128) / tpr);
+  if (2 * tile_bytes + 64 > 232448) {
+    set_error("b2_rmsnorm_fp4quant: H=%d needs the cluster reduction path, which is not built", H);
+    return B2_ERR_UNSUPPORTED;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (in_dtype == B2_DTYPE_F16) return dispatch_tpr<F16Tag>(p, tpr, s);
+  return dispatch_tpr<BF16Tag>(p, tpr, s);
+}

@@ -1,0 +1,313 @@
+"""Test and benchmark runner for the kernel modules.
+
+Keeps the public surface of the reference's tirx_kernels/runner.py that the hot path
+uses - ``run_kernel_test`` (:744-761), ``run_kernel_bench`` (:764-798), the two-stage
+``prepare_kernel_bench`` / ``run_prepared_kernel_bench`` split (:801-867),
+``prepared_gpu_benchmark`` (:98-114), ``bench`` (:492-519), ``compile_kernel`` (:735-741),
+``hardware_num_sms`` (:320-334) - and drops everything that only exists to drive TVM.
+
+Timing.  The reference delegates to ``tvm.tirx.bench.bench`` (Proton by default).  Here
+``bench`` times with CUDA events on the current stream, after a warm-up budget, zeroing a
+256 MiB buffer before every timed launch so each launch starts with a cold L2 - the same
+conditions as the reference's protocol (25 ms warm-up, 100 ms repeat, 5 rounds, mean).
+"""
+
+from __future__ import annotations
+
+import os
+import statistics
+import time
+from collections.abc import Callable, Mapping
+from dataclasses import dataclass, field
+from types import ModuleType
+from typing import Any, Protocol, runtime_checkable
+
+DEFAULT_BENCH_ROUNDS = 5
+DEFAULT_BENCH_COOLDOWN_S = 0.0
+DEFAULT_WARMUP_MS = 25
+DEFAULT_REPEAT_MS = 100
+PREPARE_NUM_SMS_ENV = "TIRX_PREPARE_NUM_SMS"
+PREPARE_CUDA_ARCH_ENV = "TIRX_PREPARE_CUDA_ARCH"
+_EXTERNAL_REFERENCES_ENV = "TIRX_INTERNAL_BENCH_REFERENCES"
+L2_FLUSH_BYTES = 256 * 1024 * 1024
+SUPPORTED_TIMERS = ("event", "event_warm")
+
+
+# ---- external references (library peers timed beside our kernels) -------------------------
+def set_external_references_enabled(enabled: bool) -> None:
+    if not isinstance(enabled, bool):
+        raise TypeError("external reference mode must be a bool")
+    os.environ[_EXTERNAL_REFERENCES_ENV] = "1" if enabled else "0"
+
+
+def external_references_enabled() -> bool:
+    return os.environ.get(_EXTERNAL_REFERENCES_ENV) == "1"
+
+
+# ---- expected-value provider ----------------------------------------------------------------
+# The reference's run_test compares with a third-party GPU kernel at test time.  This package
+# ships no expected-value generator of its own: a test harness installs one here (the
+# repository's tests install the CPU oracle); without one, run_test applies the reference's
+# self-contained checks only.
+_REFERENCE_PROVIDER: Callable[..., Any] | None = None
+
+
+def set_reference_provider(provider: Callable[..., Any] | None) -> None:
+    global _REFERENCE_PROVIDER
+    _REFERENCE_PROVIDER = provider
+
+
+def reference_provider() -> Callable[..., Any] | None:
+    return _REFERENCE_PROVIDER
+
+
+# ---- prepared benchmarks ------------------------------------------------------------------------
+@runtime_checkable
+class PreparedBenchmark(Protocol):
+    def run_gpu(self, **kwargs: Any) -> dict[str, Any]: ...
+
+
+@dataclass(frozen=True)
+class ExplicitPreparedBenchmark:
+    """Kernel-owned state prepared on the CPU and consumed by the GPU stage of the same process."""
+
+    run_gpu_fn: Callable[..., dict[str, Any]]
+    state: Any
+    required_num_gpus: int = 1
+    close_fn: Callable[[], None] | None = None
+    owner_pid: int = field(default_factory=os.getpid, init=False, repr=False)
+
+    def _check_owner(self) -> None:
+        if os.getpid() != self.owner_pid:
+            raise RuntimeError(
+                f"prepared benchmark is process-local: created in PID {self.owner_pid}, "
+                f"used in PID {os.getpid()}"
+            )
+
+    def __reduce_ex__(self, protocol: int):
+        raise TypeError("prepared benchmarks cannot be serialized across processes")
+
+    def run_gpu(self, **kwargs: Any) -> dict[str, Any]:
+        self._check_owner()
+        return self.run_gpu_fn(self.state, **kwargs)
+
+    def close(self) -> None:
+        self._check_owner()
+        if self.close_fn is not None:
+            self.close_fn()
+
+
+def prepared_gpu_benchmark(run_gpu: Callable[..., dict[str, Any]], state: Any, *,
+                           required_num_gpus: int = 1,
+                           close: Callable[[], None] | None = None) -> ExplicitPreparedBenchmark:
+    if not callable(run_gpu):
+        raise TypeError("run_gpu must be callable")
+    if isinstance(required_num_gpus, bool) or not isinstance(required_num_gpus, int):
+        raise TypeError("required_num_gpus must be an integer")
+    if required_num_gpus < 1:
+        raise ValueError("required_num_gpus must be positive")
+    if close is not None and not callable(close):
+        raise TypeError("close must be callable")
+    return ExplicitPreparedBenchmark(run_gpu, state, required_num_gpus, close)
+
+
+@dataclass(frozen=True)
+class PreparedKernelBenchmark:
+    kernel: str
+    label: str
+    benchmark: Any
+    owner_pid: int = field(default_factory=os.getpid, init=False, repr=False)
+
+    def assert_process_local(self) -> None:
+        if os.getpid() != self.owner_pid:
+            raise RuntimeError("prepared kernel benchmark used outside its preparing process")
+
+
+# ---- device facts -------------------------------------------------------------------------------
+def hardware_num_sms(default: int = 148) -> int:
+    """SM count for launch math: env override, then the live device, then the B200 value."""
+    configured = os.environ.get(PREPARE_NUM_SMS_ENV)
+    if configured is not None:
+        value = int(configured)
+        if value < 1:
+            raise ValueError(f"{PREPARE_NUM_SMS_ENV} must be positive, got {value}")
+        return value
+    import sys
+
+    torch = sys.modules.get("torch")
+    if torch is not None and torch.cuda.is_available() and torch.cuda.is_initialized():
+        return int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+    return default
+
+
+def compile_kernel(handle, *, arch: str | None = None, cuda_compile_mode: str | None = None):
+    """Resolve a module's `get_kernel` handle into its launchable executable.
+
+    The kernels are compiled ahead of time into the C-ABI library, so "compiling" binds the
+    handle's launcher and proves the library loads; `arch` other than sm_100a is rejected.
+    """
+    if arch not in (None, "sm_100a"):
+        raise ValueError(f"this build targets sm_100a only, got arch={arch!r}")
+    from tirx_kernels import _native
+
+    _native.lib()
+    launcher = handle.config.get("launcher")
+    if launcher is None:
+        raise TypeError(f"kernel handle {handle.symbol!r} carries no launcher")
+    return launcher
+
+
+# ---- timing -----------------------------------------------------------------------------------------
+def _time_one(fn: Callable[[], Any], warmup_ms: float, repeat_ms: float, flush) -> float:
+    """Mean device time of `fn` in microseconds (CUDA events, cold L2 per launch when `flush`)."""
+    import torch
+
+    fn()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(5):
+        if flush is not None:
+            flush.zero_()
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    estimate_ms = max(start.elapsed_time(end) / 5, 1e-3)
+    n_warmup = max(3, int(warmup_ms / estimate_ms))
+    n_repeat = max(5, int(repeat_ms / estimate_ms))
+    for _ in range(n_warmup):
+        fn()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(n_repeat)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(n_repeat)]
+    for i in range(n_repeat):
+        if flush is not None:
+            flush.zero_()
+        starts[i].record()
+        fn()
+        ends[i].record()
+    torch.cuda.synchronize()
+    return statistics.fmean(s.elapsed_time(e) for s, e in zip(starts, ends)) * 1e3
+
+
+def bench(funcs: Mapping[str, Callable[[], Any]], *, references: Mapping[str, Callable[[], Any]] | None = None,
+          warmup: int | None = None, repeat: int | None = None, timer: str | None = None,
+          rounds: int | None = None, cooldown_s: float | None = None, **_ignored: Any) -> dict[str, Any]:
+    """Time each launch closure; reference builders run only when references are enabled.
+
+    Returns the reference's record shape: ``impls`` (name -> mean microseconds over rounds),
+    ``round_samples``, ``errors``, ``timer`` and ``benchmark_protocol``.
+    """
+    import torch
+
+    timer = timer or "event"
+    if timer not in SUPPORTED_TIMERS:
+        raise ValueError(
+            f"timer {timer!r} needs the reference's tvm.tirx.bench; this build provides {SUPPORTED_TIMERS}"
+        )
+    warmup_ms = DEFAULT_WARMUP_MS if warmup is None else warmup
+    repeat_ms = DEFAULT_REPEAT_MS if repeat is None else repeat
+    rounds = DEFAULT_BENCH_ROUNDS if rounds is None else rounds
+    cooldown_s = DEFAULT_BENCH_COOLDOWN_S if cooldown_s is None else cooldown_s
+
+    launches: dict[str, Callable[[], Any]] = dict(funcs)
+    errors: dict[str, str] = {}
+    if references and external_references_enabled():
+        for name, builder in references.items():
+            try:
+                launches[name] = builder()
+            except Exception as error:  # a broken peer must not hide our own number
+                errors[name] = f"{type(error).__name__}: {error}"
+    flush = None
+    if timer == "event":
+        flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
+    samples: dict[str, list[float]] = {name: [] for name in launches}
+    for _ in range(rounds):
+        for name, fn in launches.items():
+            if cooldown_s:
+                time.sleep(cooldown_s)
+            samples[name].append(_time_one(fn, warmup_ms, repeat_ms, flush))
+    return {
+        "impls": {name: statistics.fmean(values) for name, values in samples.items()},
+        "round_samples": samples,
+        "errors": errors,
+        "timer": timer,
+        "benchmark_protocol": {
+            "warmup": warmup_ms,
+            "repeat": repeat_ms,
+            "cooldown_s": cooldown_s,
+            "rounds": rounds,
+            "round_aggregate": "mean",
+            "order": list(launches),
+            "l2": "flushed before every timed launch" if flush is not None else "warm",
+        },
+    }
+
+
+# ---- test / bench drivers -----------------------------------------------------------------------------
+def _params(config: dict[str, Any]) -> dict[str, Any]:
+    return {key: value for key, value in config.items() if key != "label"}
+
+
+def run_kernel_test(kernel_name: str, config: dict[str, Any], *, registry=None) -> None:
+    """Run one correctness config through the module's ``run_test``."""
+    if registry is None:
+        from tirx_kernels.registry import discover_kernels
+
+        registry = discover_kernels()
+    module = registry[kernel_name]
+    params = _params(config)
+    module.get_kernel(**params)  # the reference validates the kernel object first; ours validates the config
+    module.run_test(**params)
+
+
+def prepare_kernel_bench(kernel_name: str, config: dict[str, Any], *, module: ModuleType | None = None,
+                         require_cuda_uninitialized: bool = True) -> PreparedKernelBenchmark:
+    if module is None:
+        from tirx_kernels.registry import load_kernel
+
+        module = load_kernel(kernel_name, strict=True)
+    if require_cuda_uninitialized:
+        import sys
+
+        torch = sys.modules.get("torch")
+        if torch is not None and torch.cuda.is_initialized():
+            raise RuntimeError("CPU prepare requires a process with CUDA still uninitialized")
+    prepare = getattr(module, "prepare_bench", None)
+    if prepare is None:
+        raise TypeError(f"kernel {kernel_name!r} module {module.__name__!r} has no prepare_bench()")
+    benchmark = prepare(**_params(config))
+    if not isinstance(benchmark, PreparedBenchmark):
+        raise TypeError(f"kernel {kernel_name!r} prepare_bench() must return an object with run_gpu()")
+    return PreparedKernelBenchmark(kernel_name, config.get("label", "default"), benchmark)
+
+
+def run_prepared_kernel_bench(prepared: PreparedKernelBenchmark, *, warmup: int | None = None,
+                              repeat: int | None = None, timer: str | None = None,
+                              rounds: int | None = None, cooldown: float | None = None) -> dict[str, Any]:
+    prepared.assert_process_local()
+    given = {"warmup": warmup, "repeat": repeat, "timer": timer, "rounds": rounds, "cooldown_s": cooldown}
+    result = prepared.benchmark.run_gpu(**{k: v for k, v in given.items() if v is not None})
+    if not isinstance(result, dict):
+        result = {}
+    result.setdefault("kernel", prepared.kernel)
+    result.setdefault("label", prepared.label)
+    return result
+
+
+def close_prepared_kernel_bench(prepared: PreparedKernelBenchmark) -> None:
+    prepared.assert_process_local()
+    close = getattr(prepared.benchmark, "close", None)
+    if close is not None:
+        close()
+
+
+def run_kernel_bench(kernel_name: str, config: dict[str, Any], *, registry=None, warmup: int | None = None,
+                     repeat: int | None = None, timer: str | None = None, rounds: int | None = None,
+                     cooldown: float | None = None) -> dict[str, Any]:
+    module = None if registry is None else registry[kernel_name]
+    prepared = prepare_kernel_bench(kernel_name, config, module=module, require_cuda_uninitialized=False)
+    try:
+        return run_prepared_kernel_bench(prepared, warmup=warmup, repeat=repeat, timer=timer,
+                                         rounds=rounds, cooldown=cooldown)
+    finally:
+        close_prepared_kernel_bench(prepared)
