@@ -107,6 +107,12 @@ int b2_rmsnorm_fp4quant(const void* x, const void* w, void* y, void* sf, const f
 int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, const void* SFB,
                   const float* alpha_dev, void* D, int M, int N, int K, void* stream);
 
+/* Selects the kernel variant used by the following b2_nvfp4_gemm calls of this process
+ * (-1 restores automatic selection): 0 single CTA / N tile 128, 1 single CTA / N tile 256,
+ * 2 CTA pair / N tile 256, 3 CTA pair / N tile 128.  The reference fixes its tiling per
+ * shape in TIRX_CONFIGS, tirx_kernels/basic/nvfp4_gemm.py:860-903; this is the matching knob. */
+int b2_nvfp4_gemm_set_variant(int variant);
+
 /* Reads (and clears) the device status word written by bounded waits inside
  * b2_nvfp4_gemm on the current device; synchronises `stream` first.
  * Returns B2_OK, or B2_ERR_DEVICE_TIMEOUT with the detail in b2_last_error(). */

@@ -1,8 +1,707 @@
-// placeholder until the tcgen05 kernel lands
+// Block-scaled NVFP4 GEMM for sm_100a:  D[M,N] (bf16) = alpha * A[M,K] * B[N,K]^T.
+//
+// Semantics follow tirx_kernels/basic/nvfp4_gemm.py of the reference (operands and scale
+// layout :47-66, :941-982; one E4M3 scale per 16 values along K, fp32 accumulation,
+// alpha then bf16 in the epilogue :795-800).  The kernel itself is written from scratch:
+//
+//   * persistent CTAs (or CTA pairs), one per SM, walking a grouped tile order;
+//   * warp 0: TMA producer  - A, B and both scale-factor blocks of a 256-wide K slab
+//             land in a ring of shared-memory stages, completion counted on an mbarrier;
+//   * warp 1: MMA issuer    - copies the slab's scale factors into tensor memory with
+//             tcgen05.cp, then issues four tcgen05.mma.kind::mxf4nvf4.block_scale
+//             (K = 64 each) accumulating into TMEM; tcgen05.commit releases the stage;
+//   * warps 2-5: epilogue   - tcgen05.ld the accumulator, scale by alpha, convert to bf16
+//             and store.
+//
+// With kCtaGroup == 2 two CTAs of a cluster share one 256 x BN tile: each loads its own
+// 128 rows of A and half of B, the leader issues cta_group::2 MMAs for both.  No load
+// uses cluster multicast: every TMA load is unicast into the issuing CTA's own shared
+// memory, and cross-CTA signalling uses the cta_group::2 completion form and plain
+// remote mbarrier arrives.
+//
+// Every wait is bounded.  A wait that expires records a code in a device status word,
+// raises a CTA-wide abort flag so the other roles drain, and the kernel exits normally
+// (tensor memory released); the host reads the word through b2_nvfp4_gemm_status().
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
-extern "C" int b2_nvfp4_gemm(const void*, const void*, const void*, const void*, const float*, void*,
-                             int, int, int, void*) {
-  b2::set_error("b2_nvfp4_gemm: not built yet");
-  return B2_ERR_UNSUPPORTED;
+
+namespace b2 {
+namespace {
+
+constexpr int kBlockM = 128;        // rows of A per CTA (TMEM lanes)
+constexpr int kBlockK = 256;        // fp4 values per stage along K = 128 bytes = one swizzle row
+constexpr int kMmaK = 64;           // K per tcgen05.mma for kind::mxf4nvf4
+constexpr int kThreads = 192;       // TMA warp, MMA warp, four epilogue warps
+constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;  // one second per wait
+
+struct GemmParams {
+  const float* alpha;
+  uint16_t* D;
+  uint32_t* status;  // [0]: first failure code, [1]: detail
+  int M, N, K;
+  int tiles_m, tiles_n;  // in units of (cta_group * 128) rows and BN columns
+  int group_n;           // tile-order grouping along N
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-extern "C" int b2_nvfp4_gemm_status(void*) { return B2_OK; }
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster_acquire(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;"
+      " selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
+}
+
+template <int CG>
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  if constexpr (CG == 1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+  }
+}
+template <int CG>
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            int z, uint32_t bar) {
+  if constexpr (CG == 1) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+  }
+}
+
+template <int CG>
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  if constexpr (CG == 1)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  else
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+template <int CG>
+__device__ __forceinline__ void tmem_relinquish() {
+  if constexpr (CG == 1)
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  else
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+template <int CG>
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  if constexpr (CG == 1)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+  else
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// smem -> tmem copy of one 512-byte scale block (32 rows x 16 B), replicated to the four lane quarters
+template <int CG>
+__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint64_t desc) {
+  if constexpr (CG == 1)
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
+  else
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
+}
+template <int CG>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                       uint32_t accumulate) {
+  if constexpr (CG == 1) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p; }"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p; }"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+  }
+}
+// Makes `bar` (a shared::cluster address, possibly in the peer CTA) track completion of all
+// tcgen05 operations this thread issued so far.
+template <int CG>
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  if constexpr (CG == 1)
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  else
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- descriptors ----------------------------------------------------------------------------
+// Shared-memory matrix descriptor (sm_100 format): start address >> 4 in bits [0,14), leading
+// byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), descriptor version 1 in
+// [46,48), swizzle mode in [61,64) (0 none, 2 = 128-byte).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo16, uint32_t sbo16,
+                                              uint32_t layout) {
+  return static_cast<uint64_t>((addr >> 4) & 0x3FFFu) | (static_cast<uint64_t>(lbo16 & 0x3FFFu) << 16) |
+         (static_cast<uint64_t>(sbo16 & 0x3FFFu) << 32) | (1ull << 46) | (static_cast<uint64_t>(layout) << 61);
+}
+// K-major operand tile stored by TMA with 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t addr) { return smem_desc(addr, 1, 64, 2); }
+// One 512-byte scale block: 32 rows of 16 B, contiguous (8-row groups 128 B apart), no swizzle.
+__device__ __forceinline__ uint64_t sf_desc(uint32_t addr) { return smem_desc(addr, 0, 8, 0); }
+
+// Instruction descriptor of kind::mxf4nvf4 with block scaling: E2M1 operands (format 1) at bits 7
+// and 10, both K-major, N >> 3 at bit 17, E4M3 scales (0) at bit 23, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+  return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// ---- shared memory ------------------------------------------------------------------------------
+template <int CG, int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int kBRows = BN / CG;            // rows of B held by one CTA
+  static constexpr int kChunks = BN / 128 > 0 ? BN / 128 : 1;  // 128-row scale chunks of B
+  static constexpr int kABytes = kBlockM * 128;
+  static constexpr int kBBytes = kBRows * 128;
+  static constexpr int kSfaBytes = 4 * 512;
+  static constexpr int kSfbBytes = kChunks * 4 * 512;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+};
+
+struct WaitCtx {
+  uint32_t* status;
+  volatile uint32_t* abort_flag;  // in shared memory
+};
+
+// Bounded mbarrier wait.  Returns false after recording `code` when the barrier never flips or
+// another role of this CTA has already given up.
+template <bool kClusterAcquire = false>
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
+                                              uint32_t code) {
+  uint64_t started = 0;
+  for (uint32_t i = 0;; ++i) {
+    const bool ok = kClusterAcquire ? mbar_try_wait_cluster_acquire(bar, parity) : mbar_try_wait(bar, parity);
+    if (ok) return true;
+    if ((i & 63u) != 63u) continue;
+    if (*ctx.abort_flag) return false;
+    const uint64_t now = globaltimer_ns();
+    if (started == 0) started = now;
+    else if (now - started > kWaitBudgetNs) break;
+  }
+  if (atomicCAS(ctx.status, 0u, code) == 0u) ctx.status[1] = blockIdx.x;
+  *ctx.abort_flag = 1u;
+  return false;
+}
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int group_n, int& tm,
+                                            int& tn) {
+  const int per_group = group_n * tiles_m;
+  const int g = t / per_group;
+  const int first_n = g * group_n;
+  const int width = min(group_n, tiles_n - first_n);
+  const int local = t - g * per_group;
+  tm = local / width;
+  tn = first_n + local % width;
+}
+
+template <int CG, int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+    nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                      const __grid_constant__ GemmParams p) {
+  using L = SmemLayout<CG, BN, STAGES>;
+  constexpr int kTmemCols = 512;
+  constexpr int kSfaCol = BN;                // accumulator occupies columns [0, BN)
+  constexpr int kSfbCol = BN + 16;           // 4 K-blocks x 4 columns of SFA before it
+  static_assert(BN + 16 + 4 * 4 * L::kChunks <= kTmemCols, "tensor memory budget");
+  constexpr uint32_t kIdesc = instr_desc(kBlockM * CG, BN);
+  constexpr uint32_t kStageTx = static_cast<uint32_t>(L::kStageBytes) * CG;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + STAGES * L::kStageBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  const uint32_t tmem_full_bar = bar_base + 8u * (2 * STAGES);
+  const uint32_t tmem_empty_bar = bar_base + 8u * (2 * STAGES + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * L::kStageBytes + 8 * (2 * STAGES + 2));
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  const WaitCtx ctx{p.status, abort_flag};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;
+  const bool leader = rank == 0;
+  const int unit = CG == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int num_units = CG == 2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int k_slabs = p.K / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tmem_full_bar, 1);
+    mbar_init(tmem_empty_bar, 4 * CG);  // one arrive per epilogue warp of every CTA in the group
+    *abort_flag = 0u;
+    fence_barrier_init();
+    prefetch_tmap(&map_a);
+    prefetch_tmap(&map_b);
+    prefetch_tmap(&map_sfa);
+    prefetch_tmap(&map_sfb);
+  }
+  if (warp == 1) {
+    tmem_alloc<CG>(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish<CG>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      // With a CTA pair, transaction bytes of both CTAs are counted on the leader's barrier.
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int t = unit; t < num_tiles && alive; t += num_units) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
+        const int row_a = (tm * CG + static_cast<int>(rank)) * kBlockM;
+        const int row_b = tn * BN + static_cast<int>(rank) * L::kBRows;
+        for (int ks = 0; ks < k_slabs; ++ks) {
+          if (!wait_or_abort(empty_bar(stage), phase ^ 1u, ctx, 1u)) { alive = false; break; }
+          const uint32_t sbase = smem_base + stage * L::kStageBytes;
+          const uint32_t bar = CG == 2 ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
+          if (leader) mbar_expect_tx(full_bar(stage), kStageTx);
+          tma_load_2d<CG>(sbase, &map_a, ks * 128, row_a, bar);
+          tma_load_2d<CG>(sbase + L::kABytes, &map_b, ks * 128, row_b, bar);
+          tma_load_3d<CG>(sbase + L::kABytes + L::kBBytes, &map_sfa, 0, ks * 4, row_a / 128, bar);
+          tma_load_3d<CG>(sbase + L::kABytes + L::kBBytes + L::kSfaBytes, &map_sfb, 0, ks * 4,
+                          (tn * BN) / 128, bar);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer (leader CTA only) =================
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool alive = true;
+      for (int t = unit; t < num_tiles && alive; t += num_units) {
+        if (!wait_or_abort<CG == 2>(tmem_empty_bar, acc_phase ^ 1u, ctx, 2u)) break;
+        tc_fence_after();
+        for (int ks = 0; ks < k_slabs; ++ks) {
+          if (!wait_or_abort(full_bar(stage), phase, ctx, 3u)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t sbase = smem_base + stage * L::kStageBytes;
+          const uint32_t sfa_smem = sbase + L::kABytes + L::kBBytes;
+          const uint32_t sfb_smem = sfa_smem + L::kSfaBytes;
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            tc_cp_sf<CG>(tmem_base + kSfaCol + kb * 4, sf_desc(sfa_smem + kb * 512));
+#pragma unroll
+            for (int c = 0; c < L::kChunks; ++c)
+              tc_cp_sf<CG>(tmem_base + kSfbCol + kb * 4 * L::kChunks + c * 4,
+                           sf_desc(sfb_smem + (c * 4 + kb) * 512));
+          }
+          const uint64_t a_desc = operand_desc(sbase);
+          const uint64_t b_desc = operand_desc(sbase + L::kABytes);
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            // 64 fp4 values = 32 bytes = 2 descriptor address units inside the swizzled row
+            tc_mma<CG>(tmem_base, a_desc + 2 * kb, b_desc + 2 * kb, kIdesc, tmem_base + kSfaCol + kb * 4,
+                       tmem_base + kSfbCol + kb * 4 * L::kChunks, (ks | kb) ? 1u : 0u);
+          }
+          tc_commit<CG>(empty_bar(stage));
+          if constexpr (CG == 2) tc_commit<CG>(mapa_shared(empty_bar(stage), 1));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!alive) break;
+        tc_commit<CG>(tmem_full_bar);
+        if constexpr (CG == 2) tc_commit<CG>(mapa_shared(tmem_full_bar, 1));
+        acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ================= epilogue: warps 2..5, lane quarter = warp % 4 =================
+    const int quarter = warp & 3;
+    const float alpha = __ldg(p.alpha);
+    uint32_t acc_phase = 0;
+    const uint32_t empty_target = CG == 2 ? mapa_shared(tmem_empty_bar, 0) : tmem_empty_bar;
+    for (int t = unit; t < num_tiles; t += num_units) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
+      if (!wait_or_abort(tmem_full_bar, acc_phase, ctx, 4u)) break;
+      tc_fence_after();
+      const int row = (tm * CG + static_cast<int>(rank)) * kBlockM + quarter * 32 + lane;
+      uint16_t* drow = p.D + static_cast<int64_t>(row) * p.N + static_cast<int64_t>(tn) * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+        tmem_ld_wait();
+        if (row < p.M) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            packed[i] = pack_from_f32<BF16Tag>(__uint_as_float(v[2 * i]) * alpha,
+                                               __uint_as_float(v[2 * i + 1]) * alpha);
+          uint4* dst = reinterpret_cast<uint4*>(drow + c0);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (CG == 2) mbar_arrive_cluster(empty_target);
+        else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tmem_empty_bar) : "memory");
+      }
+      acc_phase ^= 1u;
+    }
+  }
+
+  // ---- teardown: nobody leaves while a peer may still signal into this CTA ----
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that may still be in flight time to land before shared memory is released
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  if constexpr (CG == 2) cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<CG>(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host ----------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+int encode_operand_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k / 2)};
+  const cuuint32_t box[2] = {128, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+                                       strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled(operand) failed with %d", static_cast<int>(r));
+    return B2_ERR_CUDA;
+  }
+  return B2_OK;
+}
+
+// The swizzled scale buffer is [rows/128][K/64][512 bytes]; viewed as uint16 (256, K/64, rows/128).
+int encode_scale_map(CUtensorMap* map, const void* base, int rows_padded, int k, int chunks) {
+  const cuuint64_t dims[3] = {256, static_cast<cuuint64_t>(k / 64), static_cast<cuuint64_t>(rows_padded / 128)};
+  const cuuint64_t strides[2] = {512, static_cast<cuuint64_t>(k) * 8};
+  const cuuint32_t box[3] = {256, 4, static_cast<cuuint32_t>(chunks)};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims,
+                                       strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled(scales) failed with %d", static_cast<int>(r));
+    return B2_ERR_CUDA;
+  }
+  return B2_OK;
+}
+
+struct MapKey {
+  const void *a, *b, *sfa, *sfb;
+  int m, n, k, variant;
+  bool operator==(const MapKey& o) const {
+    return a == o.a && b == o.b && sfa == o.sfa && sfb == o.sfb && m == o.m && n == o.n && k == o.k &&
+           variant == o.variant;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = 1469598103934665603ull;
+    auto mix = [&](uint64_t v) { h = (h ^ v) * 1099511628211ull; };
+    mix(reinterpret_cast<uint64_t>(k.a));
+    mix(reinterpret_cast<uint64_t>(k.b));
+    mix(reinterpret_cast<uint64_t>(k.sfa));
+    mix(reinterpret_cast<uint64_t>(k.sfb));
+    mix((static_cast<uint64_t>(k.m) << 32) ^ static_cast<uint64_t>(k.n));
+    mix((static_cast<uint64_t>(k.k) << 8) ^ static_cast<uint64_t>(k.variant));
+    return h;
+  }
+};
+struct MapSet {
+  CUtensorMap a, b, sfa, sfb;
+};
+
+std::mutex g_mu;
+std::unordered_map<MapKey, MapSet, MapKeyHash> g_maps;
+uint32_t* g_status[64] = {nullptr};
+
+// Device status word of the current device, allocated (and zeroed) on first use.
+int status_word(uint32_t** out) {
+  int dev = 0;
+  B2_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    set_error("device ordinal %d out of range", dev);
+    return B2_ERR_CUDA;
+  }
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (!g_status[dev]) {
+    uint32_t* ptr = nullptr;
+    B2_CUDA_TRY(cudaMalloc(&ptr, 2 * sizeof(uint32_t)));
+    B2_CUDA_TRY(cudaMemset(ptr, 0, 2 * sizeof(uint32_t)));
+    g_status[dev] = ptr;
+  }
+  *out = g_status[dev];
+  return B2_OK;
+}
+
+template <int CG, int BN, int STAGES>
+int launch_variant(const void* A, const void* B, const void* SFA, const void* SFB, const float* alpha,
+                   void* D, int M, int N, int K, int variant, cudaStream_t stream) {
+  using L = SmemLayout<CG, BN, STAGES>;
+  auto kernel = nvfp4_gemm_kernel<CG, BN, STAGES>;
+  uint32_t* status = nullptr;
+  if (int rc = status_word(&status)) return rc;
+
+  MapSet maps;
+  {
+    const MapKey key{A, B, SFA, SFB, M, N, K, variant};
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_maps.find(key);
+    if (it == g_maps.end()) {
+      MapSet fresh;
+      const int m_padded = (M + 127) / 128 * 128, n_padded = (N + 127) / 128 * 128;
+      if (int rc = encode_operand_map(&fresh.a, A, M, K, kBlockM)) return rc;
+      if (int rc = encode_operand_map(&fresh.b, B, N, K, L::kBRows)) return rc;
+      if (int rc = encode_scale_map(&fresh.sfa, SFA, m_padded, K, 1)) return rc;
+      if (int rc = encode_scale_map(&fresh.sfb, SFB, n_padded, K, L::kChunks)) return rc;
+      if (g_maps.size() > 4096) g_maps.clear();
+      it = g_maps.emplace(key, fresh).first;
+    }
+    maps = it->second;
+  }
+
+  GemmParams p;
+  p.alpha = alpha;
+  p.D = static_cast<uint16_t*>(D);
+  p.status = status;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.tiles_m = (M + kBlockM * CG - 1) / (kBlockM * CG);
+  p.tiles_n = N / BN;
+  p.group_n = 8;
+  const int sms = device_sm_count();
+  if (sms <= 0) return B2_ERR_CUDA;
+  const int units = std::min(p.tiles_m * p.tiles_n, sms / CG);
+
+  static bool configured = false;  // per template instantiation
+  if (!configured) {
+    B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(units * CG);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = L::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (CG == 2) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps.a, maps.b, maps.sfa, maps.sfb, p));
+  return B2_OK;
+}
+
+int g_forced_variant = -1;  // test hook: -1 = automatic
+
+}  // namespace
+}  // namespace b2
+
+// Selects a kernel variant for the following calls of this process (-1 restores automatic
+// selection).  0: single CTA, N tile 128; 1: single CTA, N tile 256; 2: CTA pair, N tile 256;
+// 3: CTA pair, N tile 128.  Used by the tests to exercise every variant on small shapes.
+extern "C" int b2_nvfp4_gemm_set_variant(int variant) {
+  if (variant < -1 || variant > 3) {
+    b2::set_error("b2_nvfp4_gemm_set_variant: unknown variant %d", variant);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  b2::g_forced_variant = variant;
+  return B2_OK;
+}
+
+extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, const void* SFB,
+                             const float* alpha_dev, void* D, int M, int N, int K, void* stream) {
+  using namespace b2;
+  if (!A || !B || !SFA || !SFB || !alpha_dev || !D) {
+    set_error("b2_nvfp4_gemm: null pointer argument");
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (M < 1 || N < 1 || K < 1 || K % 256 != 0 || N % 128 != 0) {
+    set_error("b2_nvfp4_gemm: M=%d N=%d K=%d: need M >= 1, N %% 128 == 0, K %% 256 == 0", M, N, K);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  const uintptr_t all = reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
+                        reinterpret_cast<uintptr_t>(SFA) | reinterpret_cast<uintptr_t>(SFB) |
+                        reinterpret_cast<uintptr_t>(D);
+  if (all & 15) {
+    set_error("b2_nvfp4_gemm: all tensors must be 16-byte aligned");
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (!encode_tiled_fn()) {
+    set_error("b2_nvfp4_gemm: cuTensorMapEncodeTiled is not available from this driver");
+    return B2_ERR_CUDA;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int variant = g_forced_variant;
+  if (variant < 0) {
+    const bool pair_ok = M > 128;
+    if (N % 256 == 0) variant = pair_ok ? 2 : 1;
+    else variant = pair_ok ? 3 : 0;
+  }
+  if ((variant == 1 || variant == 2) && N % 256 != 0) {
+    set_error("b2_nvfp4_gemm: variant %d needs N %% 256 == 0", variant);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  switch (variant) {
+    case 0: return launch_variant<1, 128, 6>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 0, s);
+    case 1: return launch_variant<1, 256, 4>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 1, s);
+    case 2: return launch_variant<2, 256, 5>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 2, s);
+    default: return launch_variant<2, 128, 8>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
+  }
+}
+
+extern "C" int b2_nvfp4_gemm_status(void* stream) {
+  using namespace b2;
+  uint32_t* status = nullptr;
+  if (int rc = status_word(&status)) return rc;
+  uint32_t host[2] = {0, 0};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  B2_CUDA_TRY(cudaMemcpyAsync(host, status, sizeof(host), cudaMemcpyDeviceToHost, s));
+  B2_CUDA_TRY(cudaStreamSynchronize(s));
+  if (host[0] == 0) return B2_OK;
+  B2_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(host), s));
+  static const char* const kWhat[] = {"", "producer waiting for a free stage", "MMA waiting for a drained accumulator",
+                                      "MMA waiting for a loaded stage", "epilogue waiting for the accumulator"};
+  set_error("b2_nvfp4_gemm: bounded wait expired (%s) in CTA %u",
+            host[0] < 5 ? kWhat[host[0]] : "unknown", host[1]);
+  return B2_ERR_DEVICE_TIMEOUT;
+}

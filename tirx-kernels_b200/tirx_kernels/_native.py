@@ -32,6 +32,7 @@ MAIN_SIGNATURES = {
     "b2_rmsnorm_fp4quant": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _vp]),
     "b2_nvfp4_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "b2_nvfp4_gemm_status": (_i, [_vp]),
+    "b2_nvfp4_gemm_set_variant": (_i, [_i]),
     "b2_mufu_probe": (_i, [_i, _vp, _vp, _i, _vp]),
 }
 CUBLASLT_SIGNATURES = {
@@ -143,6 +144,10 @@ def nvfp4_gemm(A, B, SFA, SFB, alpha, D, M: int, N: int, K: int) -> None:
                             current_stream_ptr()),
         "b2_nvfp4_gemm",
     )
+
+
+def nvfp4_gemm_set_variant(variant: int) -> None:
+    check(lib().b2_nvfp4_gemm_set_variant(int(variant)), "b2_nvfp4_gemm_set_variant")
 
 
 def nvfp4_gemm_status() -> None:
