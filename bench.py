@@ -1,0 +1,424 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extra]
+
+Headline (the JSON line's `value`): HBM throughput of `nvfp4_quantize` on a 16384 x 7168 bf16
+activation matrix with 0.1 % outliers, 128x4-swizzled scale factors - algorithmic bytes (input +
+packed output + scale buffer + the global scale = 300 941 316 B per launch) divided by device time.
+One step = one launch over one such batch.  With N GPUs every rank quantizes its own batch (the
+op shards by rows with no exchange: weak scaling) and `value` is the sum over ranks.
+
+The same line carries, under "extra", the other kernels of the path at their stated shapes
+(quantize 4096x7168, RMSNorm+quantize 8192x7168, GEMM 8192^3 and 16x8192x8192, and the
+N-sharded Llama-3-70B gate/up projection with its NCCL all-gather), each with its own roofline.
+
+`--impl reference` times the CPU restatement of the reference's arithmetic (oracle/, built with
+OpenMP) on the host cores on the same workload; the reference's own kernels need the TIRx
+compiler and cannot run.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+sys.path[:0] = [str(REPO / "tirx-kernels_b200"), str(REPO)]
+
+HEADLINE = {"dtype": "bfloat16", "m": 16384, "k": 7168, "sf_layout": "128x4"}
+METRIC = "nvfp4_quantize HBM throughput (16384x7168 bf16, 128x4 SF, 0.1% outliers); nvfp4_gemm TFLOPS under extra"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the ncu
+# capture summarised in profiles/ (None until a capture exists).
+HEADLINE_DRAM_TRAFFIC_BYTES = None
+
+
+def rank_env() -> tuple[int, int, int]:
+    return (int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)),
+            int(os.environ.get("WORLD_SIZE", 1)))
+
+
+# ---- clocks -------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        clocks, maxes, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                maxes.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        busy = [c for c in clocks if c > 0.5 * max(clocks)] or clocks
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(maxes), "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+# ---- data -----------------------------------------------------------------------------------------
+def headline_input(m: int, k: int, seed: int = 42):
+    """N(0,1) with 0.1 % seeded positions multiplied by 50, as bf16, plus the 448*6/amax scale (host)."""
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(m, k, generator=g, dtype=torch.float32)
+    pos = torch.randperm(m * k, generator=g)[: -(-m * k // 1000)]
+    x.view(-1)[pos] *= 50.0
+    x = x.to(torch.bfloat16)
+    gs = torch.tensor([2688.0], dtype=torch.float32) / x.float().abs().max()
+    return x, gs
+
+
+def timed_region(fn, steps: int, warmup: int, distributed: bool):
+    """Device milliseconds for `steps` calls of fn (max over ranks), after `warmup` untimed calls."""
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    if distributed:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    elapsed = torch.tensor([start.elapsed_time(end)], dtype=torch.float64, device="cuda")
+    if distributed:
+        torch.distributed.barrier()
+        torch.distributed.all_reduce(elapsed, op=torch.distributed.ReduceOp.MAX)
+    return float(elapsed.item())
+
+
+# ---- our arm ----------------------------------------------------------------------------------------
+def run_ours(args) -> dict:
+    import torch
+
+    from tirx_kernels import _checks, _native
+    from tirx_kernels.flashinfer.quantization import nvfp4_quantize as quant
+
+    rank, local_rank, world = rank_env()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    distributed = world > 1
+    if distributed:
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    _native.lib()  # fail loudly if the CUDA extension is missing
+
+    m, k, layout = HEADLINE["m"], HEADLINE["k"], HEADLINE["sf_layout"]
+    x_host, gs_host = headline_input(m, k, seed=42 + rank)
+    ex = quant.get_kernel(**HEADLINE).config["launcher"]
+    x, gs = x_host.cuda(), gs_host.cuda()
+    out, sf = quant._alloc_outputs(m, k, layout)
+    step_bytes = quant.algorithmic_bytes(m, k, layout)
+
+    def step():
+        quant._run_launch(ex, x, gs, out, sf, m, k, layout)
+
+    with ClockSampler(local_rank) as sampler:
+        elapsed_ms = timed_region(step, args.steps, args.warmup, distributed)
+    clocks = sampler.summary()
+    ms_per_step = elapsed_ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+    roofline = _checks.roofline_hbm(step_bytes, ms_per_step * 1e3)
+    roofline["traffic"] = HEADLINE_DRAM_TRAFFIC_BYTES
+
+    # end to end through the module's executable with host buffers: H2D of the batch, launch, D2H of
+    # the packed bytes and scale factors, every step
+    x_pin, out_pin, sf_pin = x_host.pin_memory(), torch.empty_like(out, device="cpu").pin_memory(), \
+        torch.empty_like(sf, device="cpu").pin_memory()
+
+    def e2e_step():
+        x.copy_(x_pin, non_blocking=True)
+        quant._run_launch(ex, x, gs, out, sf, m, k, layout)
+        out_pin.copy_(out, non_blocking=True)
+        sf_pin.copy_(sf, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_ms = timed_region(e2e_step, e2e_steps, 2, distributed) / e2e_steps
+    e2e = {"value": world * step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": x_pin.numel() * 2, "d2h_bytes_per_step": out_pin.numel() + sf_pin.numel()}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 scale math on bf16 input, e2m1/e4m3 output", "data": "synthetic",
+        "config": {"workload": "nvfp4_quantize bf16_128x4_m16384_k7168 (0.1% outliers x50), one batch per GPU",
+                   "l2": "inputs larger than L2: 301 MB touched per step, no flush needed",
+                   "algorithmic_bytes_per_step": step_bytes},
+        "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
+    }
+    if rank == 0:
+        line["cpu_baseline"] = cpu_baseline(x_host, float(gs_host.item()), layout, budget_s=8.0)
+    if not args.no_extra:
+        line["extra"] = extras(args, rank, world, distributed)
+    if distributed:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+    return line if rank == 0 else {}
+
+
+def cpu_baseline(x_host, gs: float, layout: str, budget_s: float, steps: int | None = None) -> dict:
+    """The C restatement of the reference arithmetic (OpenMP, all host cores) on the same batch."""
+    import numpy as np
+
+    from oracle import c_oracle, nvfp4_oracle
+
+    import torch
+
+    bits = x_host.contiguous().view(torch.int16).numpy().view(np.uint16)
+    m, k = bits.shape
+    step_bytes = m * k * 2 + m * k // 2 + nvfp4_oracle.sf_buffer_size(m, k // 16, layout) + 4
+    c_oracle.nvfp4_quantize(bits, "bfloat16", gs, layout)  # warm-up, loads the library
+    times = []
+    began = time.perf_counter()
+    while (steps is None and time.perf_counter() - began < budget_s) or (steps is not None and len(times) < steps):
+        t0 = time.perf_counter()
+        c_oracle.nvfp4_quantize(bits, "bfloat16", gs, layout)
+        times.append(time.perf_counter() - t0)
+        if len(times) >= 200:
+            break
+    mean = statistics.fmean(times)
+    return {"value": step_bytes / mean / 1e9, "unit": "GB/s", "cores": c_oracle.threads(), "kind": "port",
+            "sample": f"{len(times)} passes over the full {m}x{k} batch, {mean * 1e3:.1f} ms each",
+            "ms_per_step": mean * 1e3}
+
+
+# ---- the other kernels of the path -----------------------------------------------------------------------
+def _bench_us(fn, reps: int = 30, warm: int = 5) -> float:
+    import torch
+
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / reps * 1e3
+
+
+def extras(args, rank: int, world: int, distributed: bool) -> dict:
+    """Per-kernel numbers at the stated shapes.  Working sets exceed L2 or rotate over several buffer
+    sets so that launches do not hit a warm cache."""
+    import torch
+
+    from tirx_kernels import _checks, _native
+    from tirx_kernels.basic import nvfp4_gemm as gemm
+    from tirx_kernels.flashinfer.norm import rmsnorm_fp4quant as rms
+    from tirx_kernels.flashinfer.quantization import nvfp4_quantize as quant
+
+    out: dict = {}
+    if rank == 0:
+        # quantize 4096 x 7168, linear scales: 75 MB per launch < L2, so rotate over four buffer sets
+        m, k = 4096, 7168
+        sets = []
+        for i in range(4):
+            xi = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+            oi, si = quant._alloc_outputs(m, k, "linear")
+            sets.append((xi, oi, si))
+        gs1 = torch.tensor([2688.0 / 5.5], device="cuda")
+        ex1 = quant.get_kernel("bfloat16", m, k, "linear").config["launcher"]
+        state = {"i": 0}
+
+        def q1():
+            xi, oi, si = sets[state["i"] % 4]
+            state["i"] += 1
+            quant._run_launch(ex1, xi, gs1, oi, si, m, k, "linear")
+
+        us = _bench_us(q1, reps=40)
+        out["quantize_bf16_linear_m4096_k7168"] = {"us": us, "roofline": _checks.roofline_hbm(
+            quant.algorithmic_bytes(m, k, "linear"), us)}
+        del sets
+
+        # RMSNorm + quantize 8192 x 7168 (150 MB per launch > L2)
+        cfg = next(c for c in rms.BENCH_CONFIGS if c["case"] == "bench_nv_swizzled_large")
+        data, output = rms._prepare_tensors(cfg), rms._prepare_output(cfg, initialize=False)
+        exr = rms.get_kernel(**{kk: v for kk, v in cfg.items() if kk != "label"}).config["launcher"]
+        us = _bench_us(lambda: rms._launch(exr, data, output, cfg), reps=30)
+        out["rmsnorm_fp4quant_bf16_m8192_h7168_swizzled"] = {"us": us, "roofline": _checks.roofline_hbm(
+            rms.algorithmic_bytes(8192, 7168, 16, True), us)}
+        del data, output
+
+        # GEMM 8192^3 (205 MB touched per launch > L2) and the decode shape
+        for (M, N, K) in ((8192, 8192, 8192), (16, 8192, 8192)):
+            A_fp4, B_fp4, A_sf, B_sf, alpha, C_ref = gemm.prepare_data(M, N, K)
+            alpha_t = torch.tensor([float(alpha)], device="cuda")
+            D = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+            del C_ref
+            exg = gemm._compile_executable(M, N, K)
+            us = _bench_us(lambda: exg(A_fp4, B_fp4, A_sf, B_sf, alpha_t, D), reps=20 if M > 16 else 100)
+            _native.nvfp4_gemm_status()
+            entry = {"us": us, "tflops": gemm.flops(M, N, K) / us / 1e6}
+            entry["roofline"] = (_checks.roofline_nvfp4(gemm.flops(M, N, K), us) if M > 16
+                                 else _checks.roofline_hbm(gemm.algorithmic_bytes(M, N, K), us))
+            if M > 16 and args.with_cublaslt:
+                try:
+                    D2 = torch.empty_like(D)
+                    lt = lambda: _native.nvfp4_gemm_cublaslt(A_fp4, B_fp4, A_sf, B_sf, float(alpha), D2, M, N, K)
+                    us_lt = _bench_us(lt, reps=20)
+                    entry["cublaslt_us"] = us_lt
+                    entry["cublaslt_rel_fro"] = gemm.relative_frobenius_error(D, D2)
+                except Exception as error:  # the library peer is optional
+                    entry["cublaslt_error"] = str(error)[:200]
+            out[f"nvfp4_gemm_{M}x{N}x{K}"] = entry
+            del A_fp4, B_fp4, A_sf, B_sf, D
+    out["ffn_gate_up_tp"] = ffn_sharded(rank, world, distributed)
+    return out
+
+
+def ffn_sharded(rank: int, world: int, distributed: bool, M: int = 8192, N: int = 28672, K: int = 8192) -> dict:
+    """Llama-3-70B gate/up projection sharded by weight columns: every rank quantizes the full
+    activation, multiplies by its N/world shard, then an NCCL all-gather assembles the bf16 output
+    as [world, M, N/world] (strong scaling; times are the max over ranks)."""
+    import torch
+
+    from tirx_kernels import _checks, _native
+    from tirx_kernels.basic import nvfp4_gemm as gemm
+
+    shard = N // world
+    g = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    act = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, generator=torch.Generator(device="cuda").manual_seed(0))
+    w = (0.02 * torch.randn(shard, K, device="cuda", dtype=torch.float32, generator=g)).to(torch.bfloat16)
+    w_amax = w.float().abs().max().reshape(1)
+    if distributed:
+        torch.distributed.all_reduce(w_amax, op=torch.distributed.ReduceOp.MAX)
+    w_gs = 2688.0 / w_amax
+    B_fp4, B_sf = gemm.quantize_operand(w, w_gs)  # offline weight quantization, untimed
+    del w
+    a_gs = (2688.0 / act.float().abs().max()).reshape(1)
+    alpha_t = (1.0 / (a_gs * w_gs)).reshape(1).float()
+    A_fp4 = torch.empty(M, K // 2, dtype=torch.uint8, device="cuda")
+    A_sf = torch.empty(M * K // 16, dtype=torch.uint8, device="cuda")
+    D = torch.empty(M, shard, dtype=torch.bfloat16, device="cuda")
+    gathered = torch.empty(world, M, shard, dtype=torch.bfloat16, device="cuda") if distributed else None
+    exg = gemm._compile_executable(M, shard, K)
+
+    def quantize():
+        _native.nvfp4_quantize(act, A_fp4, A_sf, a_gs, M, K, "bfloat16", "128x4")
+
+    def matmul():
+        exg(A_fp4, B_fp4, A_sf, B_sf, alpha_t, D)
+
+    def gather():
+        if distributed:
+            torch.distributed.all_gather_into_tensor(gathered.view(-1), D.view(-1))
+
+    def whole():
+        quantize()
+        matmul()
+        gather()
+
+    def phase_us(fn, reps=10):
+        ms = timed_region(fn, reps, 3, distributed)
+        return ms / reps * 1e3
+
+    t_q, t_g = phase_us(quantize), phase_us(matmul)
+    t_ag = phase_us(gather) if distributed else 0.0
+    t_all = phase_us(whole)
+    _native.nvfp4_gemm_status()
+    result = {
+        "M": M, "N": N, "K": K, "world": world, "shard_n": shard,
+        "quantize_us": t_q, "gemm_us": t_g, "allgather_us": t_ag, "step_us": t_all,
+        "gemm_tflops_per_gpu": gemm.flops(M, shard, K) / t_g / 1e6,
+        "gemm_roofline": _checks.roofline_nvfp4(gemm.flops(M, shard, K), t_g),
+        "quantize_roofline": _checks.roofline_hbm(M * K * 2 + M * K // 2 + M * K // 16 + 4, t_q),
+        "total_tflops": gemm.flops(M, N, K) / t_all / 1e6, "scaling": "strong",
+    }
+    if distributed:
+        received = (world - 1) * M * shard * 2
+        result["allgather_recv_gbs"] = received / t_ag / 1e3
+        result["allgather_frac_of_770gbs_peer_copy"] = result["allgather_recv_gbs"] / 770.0
+    return result
+
+
+# ---- reference arm ------------------------------------------------------------------------------------------
+def run_reference(args) -> dict:
+    """The reference's arithmetic on the host cores (C restatement with OpenMP): one step = one full batch."""
+    rank, _, world = rank_env()
+    if rank != 0:
+        return {}
+    x_host, gs_host = headline_input(HEADLINE["m"], HEADLINE["k"])
+    base = cpu_baseline(x_host, float(gs_host.item()), HEADLINE["sf_layout"], budget_s=0.0,
+                        steps=args.steps + args.warmup)
+    return {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 scale math on bf16 input, e2m1/e4m3 output",
+        "data": "synthetic",
+        "config": {"workload": "nvfp4_quantize bf16_128x4_m16384_k7168 (0.1% outliers x50) on the host cores",
+                   "note": "the reference's GPU kernels need the TIRx compiler (tvm.tirx), absent here; this is "
+                           "the CPU restatement of its arithmetic, rank 0 only"},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--no-extra", action="store_true", help="headline only")
+    parser.add_argument("--with-cublaslt", action="store_true", help="also time the cuBLASLt NVFP4 matmul")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3)
+    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if line:
+        print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -42,6 +42,15 @@ def make_provider(native, *, prefer_c: bool = True):
             layout = "128x4" if cfg["swizzled"] else "linear"
             logical = nvfp4_oracle.logical_scales(sf, M, cols, layout)
             return torch.from_numpy(packed), torch.from_numpy(np.ascontiguousarray(logical))
+        if kernel == "nvfp4_gemm":
+            return gemm_expected(kw)
         raise KeyError(kernel)
 
     return provider
+
+
+def gemm_expected(kw) -> torch.Tensor:
+    """bf16 D of dequantize-then-fp32-matmul on the very bytes the kernel consumed."""
+    bits = nvfp4_oracle.nvfp4_gemm(kw["A_fp4"].cpu().numpy(), kw["B_fp4"].cpu().numpy(),
+                                   kw["A_sf"].cpu().numpy(), kw["B_sf"].cpu().numpy(), kw["alpha"])
+    return torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16)

@@ -158,35 +158,43 @@ def compile_kernel(handle, *, arch: str | None = None, cuda_compile_mode: str | 
 
 
 # ---- timing -----------------------------------------------------------------------------------------
+def _chain_ms(fn, n: int, flush) -> float:
+    """Device time per iteration of `n` back-to-back [flush, fn] pairs (either part optional)."""
+    import torch
+
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(n):
+        if flush is not None:
+            flush.zero_()
+        if fn is not None:
+            fn()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / n
+
+
 def _time_one(fn: Callable[[], Any], warmup_ms: float, repeat_ms: float, flush) -> float:
-    """Mean device time of `fn` in microseconds (CUDA events, cold L2 per launch when `flush`)."""
+    """Mean device time of one launch of `fn` in microseconds.
+
+    Launches are timed back to back inside one pair of CUDA events, so the cost of the events
+    themselves is amortised.  With `flush`, every launch is preceded by a write of a buffer
+    larger than L2 (cold cache), and the time of the flush alone - measured the same way - is
+    subtracted.
+    """
     import torch
 
     fn()
     torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(5):
-        if flush is not None:
-            flush.zero_()
-        fn()
-    end.record()
-    torch.cuda.synchronize()
-    estimate_ms = max(start.elapsed_time(end) / 5, 1e-3)
+    estimate_ms = max(_chain_ms(fn, 5, None), 1e-3)
     n_warmup = max(3, int(warmup_ms / estimate_ms))
-    n_repeat = max(5, int(repeat_ms / estimate_ms))
-    for _ in range(n_warmup):
-        fn()
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(n_repeat)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(n_repeat)]
-    for i in range(n_repeat):
-        if flush is not None:
-            flush.zero_()
-        starts[i].record()
-        fn()
-        ends[i].record()
-    torch.cuda.synchronize()
-    return statistics.fmean(s.elapsed_time(e) for s, e in zip(starts, ends)) * 1e3
+    n_repeat = max(10, min(2000, int(repeat_ms / estimate_ms)))
+    _chain_ms(fn, n_warmup, None)
+    if flush is None:
+        return _chain_ms(fn, n_repeat, None) * 1e3
+    both = _chain_ms(fn, n_repeat, flush)
+    alone = _chain_ms(None, n_repeat, flush)
+    return max(both - alone, 0.0) * 1e3
 
 
 def bench(funcs: Mapping[str, Callable[[], Any]], *, references: Mapping[str, Callable[[], Any]] | None = None,
