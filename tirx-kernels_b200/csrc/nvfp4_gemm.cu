@@ -41,7 +41,8 @@ constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;  // one second p
 struct GemmParams {
   const float* alpha;
   uint16_t* D;
-  uint32_t* status;  // [0]: first failure code, [1]: detail
+  uint32_t* status;  // [0]: first failure code, [1]: detail; role timers from byte 64 on
+  int profile;       // CTA 0 records per-role cycle counters when set
   int M, N, K;
   int tiles_m, tiles_n;  // in units of (cta_group * 128) rows and BN columns
   int group_n;           // tile-order grouping along N
@@ -148,6 +149,22 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 }
 
 template <int CG>
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
+                                            int w, uint32_t bar) {
+  if constexpr (CG == 1) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+        : "memory");
+  }
+}
+
+template <int CG>
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   if constexpr (CG == 1)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
@@ -168,13 +185,17 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
   else
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
-// smem -> tmem copy of one 512-byte scale block (32 rows x 16 B), replicated to the four lane quarters
+// smem -> tmem copy of 128 rows x 32 bytes into 8 consecutive TMEM columns of all 128 lanes.  Every
+// tcgen05.cp occupies the tensor pipe for about as long as an MMA regardless of its size, so
+// the scale factors are moved with the widest shape: two 512-byte scale blocks per copy.  The
+// 32-row blocks are replicated four times in shared memory by the TMA load (zero-stride
+// dimension) because each 32-lane quarter of tensor memory needs its own copy.
 template <int CG>
 __device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint64_t desc) {
   if constexpr (CG == 1)
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
+    asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
   else
-    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
+    asm volatile("tcgen05.cp.cta_group::2.128x256b [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
 }
 template <int CG>
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
@@ -230,8 +251,11 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo16, uin
 }
 // K-major operand tile stored by TMA with 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t operand_desc(uint32_t addr) { return smem_desc(addr, 1, 64, 2); }
-// One 512-byte scale block: 32 rows of 16 B, contiguous (8-row groups 128 B apart), no swizzle.
-__device__ __forceinline__ uint64_t sf_desc(uint32_t addr) { return smem_desc(addr, 0, 8, 0); }
+// Two replicated scale blocks side by side: 128 rows of 16 B each (8-row groups 128 B apart), the
+// second 16-byte column `second_offset` bytes after the first, no swizzle.
+__device__ __forceinline__ uint64_t sf_desc(uint32_t addr, uint32_t second_offset) {
+  return smem_desc(addr, second_offset >> 4, 8, 0);
+}
 
 // Instruction descriptor of kind::mxf4nvf4 with block scaling: E2M1 operands (format 1) at bits 7
 // and 10, both K-major, N >> 3 at bit 17, E4M3 scales (0) at bit 23, M >> 4 at bit 24.
@@ -246,8 +270,9 @@ struct SmemLayout {
   static constexpr int kChunks = BN / 128 > 0 ? BN / 128 : 1;  // 128-row scale chunks of B
   static constexpr int kABytes = kBlockM * 128;
   static constexpr int kBBytes = kBRows * 128;
-  static constexpr int kSfaBytes = 4 * 512;
-  static constexpr int kSfbBytes = kChunks * 4 * 512;
+  static constexpr int kSfImage = 4 * 512;             // one scale block replicated for the 4 lane quarters
+  static constexpr int kSfaBytes = 4 * kSfImage;       // 4 K-blocks of 64
+  static constexpr int kSfbBytes = kChunks * 4 * kSfImage;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
@@ -354,23 +379,32 @@ __global__ void __launch_bounds__(kThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
+      const bool prof = p.profile && blockIdx.x == 0;
+      long long t_wait = 0, t_begin = prof ? clock64() : 0;
       for (int t = unit; t < num_tiles && alive; t += num_units) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
         const int row_a = (tm * CG + static_cast<int>(rank)) * kBlockM;
         const int row_b = tn * BN + static_cast<int>(rank) * L::kBRows;
         for (int ks = 0; ks < k_slabs; ++ks) {
+          const long long w0 = prof ? clock64() : 0;
           if (!wait_or_abort(empty_bar(stage), phase ^ 1u, ctx, 1u)) { alive = false; break; }
+          if (prof) t_wait += clock64() - w0;
           const uint32_t sbase = smem_base + stage * L::kStageBytes;
           const uint32_t bar = CG == 2 ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
           if (leader) mbar_expect_tx(full_bar(stage), kStageTx);
           tma_load_2d<CG>(sbase, &map_a, ks * 128, row_a, bar);
           tma_load_2d<CG>(sbase + L::kABytes, &map_b, ks * 128, row_b, bar);
-          tma_load_3d<CG>(sbase + L::kABytes + L::kBBytes, &map_sfa, 0, ks * 4, row_a / 128, bar);
-          tma_load_3d<CG>(sbase + L::kABytes + L::kBBytes + L::kSfaBytes, &map_sfb, 0, ks * 4,
+          tma_load_4d<CG>(sbase + L::kABytes + L::kBBytes, &map_sfa, 0, 0, ks * 4, row_a / 128, bar);
+          tma_load_4d<CG>(sbase + L::kABytes + L::kBBytes + L::kSfaBytes, &map_sfb, 0, 0, ks * 4,
                           (tn * BN) / 128, bar);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
+      }
+      if (prof) {
+        unsigned long long* c = reinterpret_cast<unsigned long long*>(p.status + 16);
+        c[0] = t_wait;
+        c[1] = clock64() - t_begin;
       }
     }
   } else if (warp == 1) {
@@ -379,22 +413,35 @@ __global__ void __launch_bounds__(kThreads, 1)
       int stage = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool alive = true;
+      const bool prof = p.profile && blockIdx.x == 0;
+      long long t_full = 0, t_acc = 0, t_issue = 0, t_begin = prof ? clock64() : 0;
       for (int t = unit; t < num_tiles && alive; t += num_units) {
+        const long long a0 = prof ? clock64() : 0;
         if (!wait_or_abort<CG == 2>(tmem_empty_bar, acc_phase ^ 1u, ctx, 2u)) break;
+        if (prof) t_acc += clock64() - a0;
         tc_fence_after();
         for (int ks = 0; ks < k_slabs; ++ks) {
+          const long long w0 = prof ? clock64() : 0;
           if (!wait_or_abort(full_bar(stage), phase, ctx, 3u)) { alive = false; break; }
+          const long long w1 = prof ? clock64() : 0;
+          t_full += w1 - w0;
           tc_fence_after();
           const uint32_t sbase = smem_base + stage * L::kStageBytes;
           const uint32_t sfa_smem = sbase + L::kABytes + L::kBBytes;
           const uint32_t sfb_smem = sfa_smem + L::kSfaBytes;
+          // Scale factors: shared memory holds [chunk][k-block][4 replicas][512 B].  SFA columns are
+          // k-block major (4 per k-block); SFB columns are k-block major, then 128-row chunk.
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb) {
-            tc_cp_sf<CG>(tmem_base + kSfaCol + kb * 4, sf_desc(sfa_smem + kb * 512));
+          for (int j = 0; j < 2; ++j)
+            tc_cp_sf<CG>(tmem_base + kSfaCol + j * 8, sf_desc(sfa_smem + 2 * j * L::kSfImage, L::kSfImage));
+          if constexpr (L::kChunks == 1) {
 #pragma unroll
-            for (int c = 0; c < L::kChunks; ++c)
-              tc_cp_sf<CG>(tmem_base + kSfbCol + kb * 4 * L::kChunks + c * 4,
-                           sf_desc(sfb_smem + (c * 4 + kb) * 512));
+            for (int j = 0; j < 2; ++j)
+              tc_cp_sf<CG>(tmem_base + kSfbCol + j * 8, sf_desc(sfb_smem + 2 * j * L::kSfImage, L::kSfImage));
+          } else {
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb)
+              tc_cp_sf<CG>(tmem_base + kSfbCol + kb * 8, sf_desc(sfb_smem + kb * L::kSfImage, 4 * L::kSfImage));
           }
           const uint64_t a_desc = operand_desc(sbase);
           const uint64_t b_desc = operand_desc(sbase + L::kABytes);
@@ -406,12 +453,20 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           tc_commit<CG>(empty_bar(stage));
           if constexpr (CG == 2) tc_commit<CG>(mapa_shared(empty_bar(stage), 1));
+          if (prof) t_issue += clock64() - w1;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!alive) break;
         tc_commit<CG>(tmem_full_bar);
         if constexpr (CG == 2) tc_commit<CG>(mapa_shared(tmem_full_bar, 1));
         acc_phase ^= 1u;
+      }
+      if (prof) {
+        unsigned long long* c = reinterpret_cast<unsigned long long*>(p.status + 16);
+        c[2] = t_full;
+        c[3] = t_acc;
+        c[4] = clock64() - t_begin;
+        c[5] = t_issue;
       }
     }
   } else {
@@ -420,29 +475,30 @@ __global__ void __launch_bounds__(kThreads, 1)
     const float alpha = __ldg(p.alpha);
     uint32_t acc_phase = 0;
     const uint32_t empty_target = CG == 2 ? mapa_shared(tmem_empty_bar, 0) : tmem_empty_bar;
+    const bool prof = p.profile && blockIdx.x == 0 && threadIdx.x == 64;
+    long long t_wait = 0, t_body = 0, n_tiles = 0;
     for (int t = unit; t < num_tiles; t += num_units) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
+      const long long w0 = prof ? clock64() : 0;
       if (!wait_or_abort(tmem_full_bar, acc_phase, ctx, 4u)) break;
+      const long long w1 = prof ? clock64() : 0;
+      t_wait += w1 - w0;
       tc_fence_after();
       const int row = (tm * CG + static_cast<int>(rank)) * kBlockM + quarter * 32 + lane;
       uint16_t* drow = p.D + static_cast<int64_t>(row) * p.N + static_cast<int64_t>(tn) * BN;
-#pragma unroll 1
+      // Drain the accumulator row into registers as packed bf16, hand tensor memory back to the
+      // MMA warp, and only then write to global memory, so the next tile's MMAs overlap the stores.
+      uint32_t packed[BN / 2];
+#pragma unroll
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t v[32];
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
         tmem_ld_wait();
-        if (row < p.M) {
-          uint32_t packed[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            packed[i] = pack_from_f32<BF16Tag>(__uint_as_float(v[2 * i]) * alpha,
-                                               __uint_as_float(v[2 * i + 1]) * alpha);
-          uint4* dst = reinterpret_cast<uint4*>(drow + c0);
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-        }
+        for (int i = 0; i < 16; ++i)
+          packed[c0 / 2 + i] = pack_from_f32<BF16Tag>(__uint_as_float(v[2 * i]) * alpha,
+                                                      __uint_as_float(v[2 * i + 1]) * alpha);
       }
       tc_fence_before();
       __syncwarp();
@@ -450,7 +506,20 @@ __global__ void __launch_bounds__(kThreads, 1)
         if constexpr (CG == 2) mbar_arrive_cluster(empty_target);
         else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tmem_empty_bar) : "memory");
       }
+      if (row < p.M) {
+        uint4* dst = reinterpret_cast<uint4*>(drow);
+#pragma unroll
+        for (int i = 0; i < BN / 8; ++i)
+          dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+      }
       acc_phase ^= 1u;
+      if (prof) { t_body += clock64() - w1; ++n_tiles; }
+    }
+    if (prof) {
+      unsigned long long* c = reinterpret_cast<unsigned long long*>(p.status + 16);
+      c[6] = t_wait;
+      c[7] = t_body;
+      c[8] = n_tiles;
     }
   }
 
@@ -503,13 +572,15 @@ int encode_operand_map(CUtensorMap* map, const void* base, int rows, int k, int 
   return B2_OK;
 }
 
-// The swizzled scale buffer is [rows/128][K/64][512 bytes]; viewed as uint16 (256, K/64, rows/128).
+// The swizzled scale buffer is [rows/128][K/64][512 bytes].  Viewed as uint16 with an extra
+// zero-stride dimension, (256, 4 replicas, K/64, rows/128), one load of box (256, 4, 4, chunks)
+// lands in shared memory as [chunk][k-block][replica][512 B].
 int encode_scale_map(CUtensorMap* map, const void* base, int rows_padded, int k, int chunks) {
-  const cuuint64_t dims[3] = {256, static_cast<cuuint64_t>(k / 64), static_cast<cuuint64_t>(rows_padded / 128)};
-  const cuuint64_t strides[2] = {512, static_cast<cuuint64_t>(k) * 8};
-  const cuuint32_t box[3] = {256, 4, static_cast<cuuint32_t>(chunks)};
-  const cuuint32_t elem[3] = {1, 1, 1};
-  const CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims,
+  const cuuint64_t dims[4] = {256, 4, static_cast<cuuint64_t>(k / 64), static_cast<cuuint64_t>(rows_padded / 128)};
+  const cuuint64_t strides[3] = {0, 512, static_cast<cuuint64_t>(k) * 8};
+  const cuuint32_t box[4] = {256, 4, 4, static_cast<cuuint32_t>(chunks)};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  const CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims,
                                        strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -548,6 +619,9 @@ struct MapSet {
 std::mutex g_mu;
 std::unordered_map<MapKey, MapSet, MapKeyHash> g_maps;
 uint32_t* g_status[64] = {nullptr};
+constexpr int kStatusWords = 64;  // 2 status words, padding, 9 64-bit role timers from word 16
+int g_profile = 0;
+
 
 // Device status word of the current device, allocated (and zeroed) on first use.
 int status_word(uint32_t** out) {
@@ -560,8 +634,8 @@ int status_word(uint32_t** out) {
   std::lock_guard<std::mutex> lock(g_mu);
   if (!g_status[dev]) {
     uint32_t* ptr = nullptr;
-    B2_CUDA_TRY(cudaMalloc(&ptr, 2 * sizeof(uint32_t)));
-    B2_CUDA_TRY(cudaMemset(ptr, 0, 2 * sizeof(uint32_t)));
+    B2_CUDA_TRY(cudaMalloc(&ptr, kStatusWords * sizeof(uint32_t)));
+    B2_CUDA_TRY(cudaMemset(ptr, 0, kStatusWords * sizeof(uint32_t)));
     g_status[dev] = ptr;
   }
   *out = g_status[dev];
@@ -598,6 +672,7 @@ int launch_variant(const void* A, const void* B, const void* SFA, const void* SF
   p.alpha = alpha;
   p.D = static_cast<uint16_t*>(D);
   p.status = status;
+  p.profile = g_profile;
   p.M = M;
   p.N = N;
   p.K = K;
@@ -682,11 +757,27 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
     return B2_ERR_INVALID_ARGUMENT;
   }
   switch (variant) {
-    case 0: return launch_variant<1, 128, 6>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 0, s);
-    case 1: return launch_variant<1, 256, 4>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 1, s);
-    case 2: return launch_variant<2, 256, 5>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 2, s);
-    default: return launch_variant<2, 128, 8>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
+    case 0: return launch_variant<1, 128, 4>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 0, s);
+    case 1: return launch_variant<1, 256, 3>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 1, s);
+    case 2: return launch_variant<2, 256, 4>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 2, s);
+    default: return launch_variant<2, 128, 5>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
   }
+}
+
+// Role timers of CTA 0 for the most recent profiled launch (SM cycles): producer wait-for-free-stage,
+// producer total, MMA wait-for-data, MMA wait-for-accumulator, MMA total, MMA issue, epilogue
+// wait-for-accumulator, epilogue body, tiles.  `enable` switches recording for later launches.
+extern "C" int b2_nvfp4_gemm_role_timers(int enable, unsigned long long* out9, void* stream) {
+  using namespace b2;
+  uint32_t* status = nullptr;
+  if (int rc = status_word(&status)) return rc;
+  g_profile = enable ? 1 : 0;
+  if (out9) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    B2_CUDA_TRY(cudaMemcpyAsync(out9, status + 16, 9 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s));
+    B2_CUDA_TRY(cudaStreamSynchronize(s));
+  }
+  return B2_OK;
 }
 
 extern "C" int b2_nvfp4_gemm_status(void* stream) {
