@@ -34,8 +34,7 @@ namespace {
 
 constexpr int kBlockM = 128;        // rows of A per CTA (TMEM lanes)
 constexpr int kBlockK = 256;        // fp4 values per stage along K = 128 bytes = one swizzle row
-constexpr int kMmaK = 64;           // K per tcgen05.mma for kind::mxf4nvf4
-constexpr int kThreads = 192;       // TMA warp, MMA warp, four epilogue warps
+constexpr int kThreads = 576;       // TMA warp, MMA warp, 2 x 4 scale warps, 8 epilogue warps
 constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;  // one second per wait
 
 struct GemmParams {
@@ -78,6 +77,14 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
                : "memory");
 }
+// Remote arrive without memory ordering: for hand-offs whose payload lives in tensor memory and
+// has already been completed with tcgen05.wait, so no generic-proxy writes need publishing.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_local(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -99,9 +106,6 @@ __device__ __forceinline__ bool mbar_try_wait_cluster_acquire(uint32_t bar, uint
 }
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -149,22 +153,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 }
 
 template <int CG>
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
-                                            int w, uint32_t bar) {
-  if constexpr (CG == 1) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
-        : "memory");
-  } else {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
-        : "memory");
-  }
-}
-
-template <int CG>
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   if constexpr (CG == 1)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
@@ -184,18 +172,6 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
   else
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-// smem -> tmem copy of 128 rows x 32 bytes into 8 consecutive TMEM columns of all 128 lanes.  Every
-// tcgen05.cp occupies the tensor pipe for about as long as an MMA regardless of its size, so
-// the scale factors are moved with the widest shape: two 512-byte scale blocks per copy.  The
-// 32-row blocks are replicated four times in shared memory by the TMA load (zero-stride
-// dimension) because each 32-lane quarter of tensor memory needs its own copy.
-template <int CG>
-__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint64_t desc) {
-  if constexpr (CG == 1)
-    asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
-  else
-    asm volatile("tcgen05.cp.cta_group::2.128x256b [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
 }
 template <int CG>
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
@@ -251,12 +227,6 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo16, uin
 }
 // K-major operand tile stored by TMA with 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t operand_desc(uint32_t addr) { return smem_desc(addr, 1, 64, 2); }
-// Two replicated scale blocks side by side: 128 rows of 16 B each (8-row groups 128 B apart), the
-// second 16-byte column `second_offset` bytes after the first, no swizzle.
-__device__ __forceinline__ uint64_t sf_desc(uint32_t addr, uint32_t second_offset) {
-  return smem_desc(addr, second_offset >> 4, 8, 0);
-}
-
 // Instruction descriptor of kind::mxf4nvf4 with block scaling: E2M1 operands (format 1) at bits 7
 // and 10, both K-major, N >> 3 at bit 17, E4M3 scales (0) at bit 23, M >> 4 at bit 24.
 __host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
@@ -266,16 +236,18 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
 // ---- shared memory ------------------------------------------------------------------------------
 template <int CG, int BN, int STAGES>
 struct SmemLayout {
-  static constexpr int kBRows = BN / CG;            // rows of B held by one CTA
+  static constexpr int kBRows = BN / CG;                       // rows of B held by one CTA
   static constexpr int kChunks = BN / 128 > 0 ? BN / 128 : 1;  // 128-row scale chunks of B
   static constexpr int kABytes = kBlockM * 128;
   static constexpr int kBBytes = kBRows * 128;
-  static constexpr int kSfImage = 4 * 512;             // one scale block replicated for the 4 lane quarters
-  static constexpr int kSfaBytes = 4 * kSfImage;       // 4 K-blocks of 64
-  static constexpr int kSfbBytes = kChunks * 4 * kSfImage;
+  static constexpr int kSfaBytes = 4 * 512;                    // 4 K-blocks of 64, 512 B each
+  static constexpr int kSfbBytes = kChunks * 4 * 512;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSfCols = 16 + 16 * kChunks;            // TMEM columns of one stage's scales
+  static constexpr int kBarrierBytes = 512;
   static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  static_assert(BN + STAGES * kSfCols <= 512, "tensor memory budget");
+  static_assert((4 * STAGES + 2) * 8 + 16 <= kBarrierBytes, "barrier area");
 };
 
 struct WaitCtx {
@@ -314,6 +286,25 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = first_n + local % width;
 }
 
+__device__ __forceinline__ void lds128(uint32_t addr, uint32_t* r) {
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// registers -> tensor memory: lane i of the warp writes 16 consecutive columns of TMEM lane (base + i)
+__device__ __forceinline__ void tmem_st_32x32_x16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Warp roles.  The scale and epilogue warps are placed so that (warp & 3) is the 32-lane quarter of
+// tensor memory the warp is allowed to touch.
+constexpr int kWarpProducer = 0, kWarpMma = 1, kWarpScale0 = 2, kWarpEpi0 = 10;
+
 template <int CG, int BN, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -321,21 +312,24 @@ __global__ void __launch_bounds__(kThreads, 1)
                       const __grid_constant__ GemmParams p) {
   using L = SmemLayout<CG, BN, STAGES>;
   constexpr int kTmemCols = 512;
-  constexpr int kSfaCol = BN;                // accumulator occupies columns [0, BN)
-  constexpr int kSfbCol = BN + 16;           // 4 K-blocks x 4 columns of SFA before it
-  static_assert(BN + 16 + 4 * 4 * L::kChunks <= kTmemCols, "tensor memory budget");
   constexpr uint32_t kIdesc = instr_desc(kBlockM * CG, BN);
-  constexpr uint32_t kStageTx = static_cast<uint32_t>(L::kStageBytes) * CG;
+  constexpr uint32_t kOperandTx = static_cast<uint32_t>(L::kABytes + L::kBBytes) * CG;
+  constexpr uint32_t kScaleTx = static_cast<uint32_t>(L::kSfaBytes + L::kSfbBytes);
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t bar_base = smem_base + STAGES * L::kStageBytes;
+  // full: A and B of a stage landed (CTA pair: counted on the leader for both CTAs);
+  // sfload: this CTA's scale blocks landed; sfready: scales are in tensor memory (on the leader,
+  // one arrive per scale warp of the group); empty: the stage's MMAs retired.
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  const uint32_t tmem_full_bar = bar_base + 8u * (2 * STAGES);
-  const uint32_t tmem_empty_bar = bar_base + 8u * (2 * STAGES + 1);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * L::kStageBytes + 8 * (2 * STAGES + 2));
+  auto sfload_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto sfready_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (3 * STAGES + s); };
+  const uint32_t tmem_full_bar = bar_base + 8u * (4 * STAGES);
+  const uint32_t tmem_empty_bar = bar_base + 8u * (4 * STAGES + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * L::kStageBytes + 8 * (4 * STAGES + 2));
   volatile uint32_t* abort_flag = tmem_slot + 1;
   const WaitCtx ctx{p.status, abort_flag};
 
@@ -347,14 +341,18 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int num_units = CG == 2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int k_slabs = p.K / kBlockK;
+  const bool prof = p.profile && blockIdx.x == 0 && lane == 0;
+  unsigned long long* counters = reinterpret_cast<unsigned long long*>(p.status + 16);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
+      mbar_init(sfload_bar(s), 1);
+      mbar_init(sfready_bar(s), 4 * CG);
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(tmem_full_bar, 1);
-    mbar_init(tmem_empty_bar, 4 * CG);  // one arrive per epilogue warp of every CTA in the group
+    mbar_init(tmem_empty_bar, 8 * CG);  // one arrive per epilogue warp of every CTA in the group
     *abort_flag = 0u;
     fence_barrier_init();
     prefetch_tmap(&map_a);
@@ -362,7 +360,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     prefetch_tmap(&map_sfa);
     prefetch_tmap(&map_sfb);
   }
-  if (warp == 1) {
+  if (warp == kWarpMma) {
     tmem_alloc<CG>(smem_u32(tmem_slot), kTmemCols);
     tmem_relinquish<CG>();
   }
@@ -372,14 +370,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == kWarpProducer) {
     // ================= TMA producer =================
     if (lane == 0) {
-      // With a CTA pair, transaction bytes of both CTAs are counted on the leader's barrier.
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      const bool prof = p.profile && blockIdx.x == 0;
       long long t_wait = 0, t_begin = prof ? clock64() : 0;
       for (int t = unit; t < num_tiles && alive; t += num_units) {
         int tm, tn;
@@ -391,30 +387,31 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (!wait_or_abort(empty_bar(stage), phase ^ 1u, ctx, 1u)) { alive = false; break; }
           if (prof) t_wait += clock64() - w0;
           const uint32_t sbase = smem_base + stage * L::kStageBytes;
-          const uint32_t bar = CG == 2 ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
-          if (leader) mbar_expect_tx(full_bar(stage), kStageTx);
-          tma_load_2d<CG>(sbase, &map_a, ks * 128, row_a, bar);
-          tma_load_2d<CG>(sbase + L::kABytes, &map_b, ks * 128, row_b, bar);
-          tma_load_4d<CG>(sbase + L::kABytes + L::kBBytes, &map_sfa, 0, 0, ks * 4, row_a / 128, bar);
-          tma_load_4d<CG>(sbase + L::kABytes + L::kBBytes + L::kSfaBytes, &map_sfb, 0, 0, ks * 4,
-                          (tn * BN) / 128, bar);
+          // operand bytes of both CTAs of a pair are counted on the leader's barrier
+          const uint32_t op_bar = CG == 2 ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
+          if (leader) mbar_expect_tx(full_bar(stage), kOperandTx);
+          mbar_expect_tx(sfload_bar(stage), kScaleTx);
+          tma_load_3d<1>(sbase + L::kABytes + L::kBBytes, &map_sfa, 0, ks * 4, row_a / 128, sfload_bar(stage));
+          tma_load_3d<1>(sbase + L::kABytes + L::kBBytes + L::kSfaBytes, &map_sfb, 0, ks * 4, (tn * BN) / 128,
+                         sfload_bar(stage));
+          tma_load_2d<CG>(sbase, &map_a, ks * 128, row_a, op_bar);
+          tma_load_2d<CG>(sbase + L::kABytes, &map_b, ks * 128, row_b, op_bar);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
       if (prof) {
-        unsigned long long* c = reinterpret_cast<unsigned long long*>(p.status + 16);
-        c[0] = t_wait;
-        c[1] = clock64() - t_begin;
+        counters[0] = t_wait;
+        counters[1] = clock64() - t_begin;
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kWarpMma) {
     // ================= MMA issuer (leader CTA only) =================
     if (leader && lane == 0) {
       int stage = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool alive = true;
-      const bool prof = p.profile && blockIdx.x == 0;
       long long t_full = 0, t_acc = 0, t_issue = 0, t_begin = prof ? clock64() : 0;
+      const uint64_t ns_begin = prof ? globaltimer_ns() : 0;
       for (int t = unit; t < num_tiles && alive; t += num_units) {
         const long long a0 = prof ? clock64() : 0;
         if (!wait_or_abort<CG == 2>(tmem_empty_bar, acc_phase ^ 1u, ctx, 2u)) break;
@@ -422,34 +419,20 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_after();
         for (int ks = 0; ks < k_slabs; ++ks) {
           const long long w0 = prof ? clock64() : 0;
+          if (!wait_or_abort<CG == 2>(sfready_bar(stage), phase, ctx, 6u)) { alive = false; break; }
           if (!wait_or_abort(full_bar(stage), phase, ctx, 3u)) { alive = false; break; }
           const long long w1 = prof ? clock64() : 0;
           t_full += w1 - w0;
           tc_fence_after();
           const uint32_t sbase = smem_base + stage * L::kStageBytes;
-          const uint32_t sfa_smem = sbase + L::kABytes + L::kBBytes;
-          const uint32_t sfb_smem = sfa_smem + L::kSfaBytes;
-          // Scale factors: shared memory holds [chunk][k-block][4 replicas][512 B].  SFA columns are
-          // k-block major (4 per k-block); SFB columns are k-block major, then 128-row chunk.
-#pragma unroll
-          for (int j = 0; j < 2; ++j)
-            tc_cp_sf<CG>(tmem_base + kSfaCol + j * 8, sf_desc(sfa_smem + 2 * j * L::kSfImage, L::kSfImage));
-          if constexpr (L::kChunks == 1) {
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-              tc_cp_sf<CG>(tmem_base + kSfbCol + j * 8, sf_desc(sfb_smem + 2 * j * L::kSfImage, L::kSfImage));
-          } else {
-#pragma unroll
-            for (int kb = 0; kb < 4; ++kb)
-              tc_cp_sf<CG>(tmem_base + kSfbCol + kb * 8, sf_desc(sfb_smem + kb * L::kSfImage, 4 * L::kSfImage));
-          }
+          const uint32_t sf_tmem = tmem_base + BN + stage * L::kSfCols;
           const uint64_t a_desc = operand_desc(sbase);
           const uint64_t b_desc = operand_desc(sbase + L::kABytes);
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) {
             // 64 fp4 values = 32 bytes = 2 descriptor address units inside the swizzled row
-            tc_mma<CG>(tmem_base, a_desc + 2 * kb, b_desc + 2 * kb, kIdesc, tmem_base + kSfaCol + kb * 4,
-                       tmem_base + kSfbCol + kb * 4 * L::kChunks, (ks | kb) ? 1u : 0u);
+            tc_mma<CG>(tmem_base, a_desc + 2 * kb, b_desc + 2 * kb, kIdesc, sf_tmem + kb * 4,
+                       sf_tmem + 16 + kb * 4 * L::kChunks, (ks | kb) ? 1u : 0u);
           }
           tc_commit<CG>(empty_bar(stage));
           if constexpr (CG == 2) tc_commit<CG>(mapa_shared(empty_bar(stage), 1));
@@ -462,38 +445,90 @@ __global__ void __launch_bounds__(kThreads, 1)
         acc_phase ^= 1u;
       }
       if (prof) {
-        unsigned long long* c = reinterpret_cast<unsigned long long*>(p.status + 16);
-        c[2] = t_full;
-        c[3] = t_acc;
-        c[4] = clock64() - t_begin;
-        c[5] = t_issue;
+        counters[2] = t_full;
+        counters[3] = t_acc;
+        counters[4] = clock64() - t_begin;
+        counters[5] = t_issue;
+        counters[11] = globaltimer_ns() - ns_begin;
       }
     }
-  } else {
-    // ================= epilogue: warps 2..5, lane quarter = warp % 4 =================
+  } else if (warp < kWarpEpi0) {
+    // ================= scale warps: shared memory -> registers -> tensor memory =================
+    // tcgen05.cp would do this copy inside the tensor pipe, where every copy displaces an MMA for
+    // about as long as an MMA takes; going through registers keeps the pipe for the MMAs alone.
+    // TMEM lane L, column 4*kb + j of a stage's scale area holds the four scales (one per 16-wide
+    // K block of k-block kb) of tile row 32*j + L % 32, i.e. 16-byte row L % 32 of the 512-byte
+    // swizzled block; every 32-lane quarter carries the same data.
+    // Two sets of four warps share the K slabs, so one set's wait for its TMEM stores overlaps
+    // the other set's shared-memory reads.  A set owns the stages of one parity: it then
+    // observes every phase of the barriers it waits on (a waiter that skipped a phase could not
+    // tell the phase it wants from the one two before it).
     const int quarter = warp & 3;
+    const int set = (warp - kWarpScale0) >> 2;
+    const bool sprof = prof && warp == kWarpScale0;
+    long long t_wait = 0, t_body = 0;
+    const int total_slabs = ((num_tiles - unit + num_units - 1) / num_units) * k_slabs;
+    for (int n = 0; n < total_slabs; ++n) {
+      const int stage = n % STAGES;
+      if ((stage & 1) != set) continue;
+      const uint32_t phase = static_cast<uint32_t>(n / STAGES) & 1u;
+      const long long w0 = sprof ? clock64() : 0;
+      if (!wait_or_abort(sfload_bar(stage), phase, ctx, 5u)) break;
+      const long long w1 = sprof ? clock64() : 0;
+      const uint32_t sfa_smem = smem_base + stage * L::kStageBytes + L::kABytes + L::kBBytes + lane * 16;
+      const uint32_t sfb_smem = sfa_smem + L::kSfaBytes;
+      uint32_t a[16], b[16 * L::kChunks];
+#pragma unroll
+      for (int kb = 0; kb < 4; ++kb) lds128(sfa_smem + kb * 512, a + 4 * kb);
+#pragma unroll
+      for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+        for (int c = 0; c < L::kChunks; ++c) lds128(sfb_smem + (c * 4 + kb) * 512, b + 4 * (kb * L::kChunks + c));
+      const uint32_t dst = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + BN + stage * L::kSfCols;
+      tmem_st_32x32_x16(dst, a);
+#pragma unroll
+      for (int c = 0; c < L::kChunks; ++c) tmem_st_32x32_x16(dst + 16 + 16 * c, b + 16 * c);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (leader) mbar_arrive_local(sfready_bar(stage));
+        else mbar_arrive_cluster_relaxed(mapa_shared(sfready_bar(stage), 0));
+      }
+      if (sprof) { t_wait += w1 - w0; t_body += clock64() - w1; }
+    }
+    if (sprof) {
+      counters[9] = t_wait;
+      counters[10] = t_body;
+    }
+  } else {
+    // ================= epilogue: 8 warps, lane quarter = warp & 3, column half = (warp - 10) / 4 ===========
+    constexpr int kHalf = BN / 2;
+    const int quarter = warp & 3;
+    const int half = (warp - kWarpEpi0) >> 2;
     const float alpha = __ldg(p.alpha);
     uint32_t acc_phase = 0;
     const uint32_t empty_target = CG == 2 ? mapa_shared(tmem_empty_bar, 0) : tmem_empty_bar;
-    const bool prof = p.profile && blockIdx.x == 0 && threadIdx.x == 64;
+    const bool eprof = prof && warp == kWarpEpi0;
     long long t_wait = 0, t_body = 0, n_tiles = 0;
     for (int t = unit; t < num_tiles; t += num_units) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
-      const long long w0 = prof ? clock64() : 0;
+      const long long w0 = eprof ? clock64() : 0;
       if (!wait_or_abort(tmem_full_bar, acc_phase, ctx, 4u)) break;
-      const long long w1 = prof ? clock64() : 0;
+      const long long w1 = eprof ? clock64() : 0;
       t_wait += w1 - w0;
       tc_fence_after();
       const int row = (tm * CG + static_cast<int>(rank)) * kBlockM + quarter * 32 + lane;
-      uint16_t* drow = p.D + static_cast<int64_t>(row) * p.N + static_cast<int64_t>(tn) * BN;
-      // Drain the accumulator row into registers as packed bf16, hand tensor memory back to the
-      // MMA warp, and only then write to global memory, so the next tile's MMAs overlap the stores.
-      uint32_t packed[BN / 2];
+      uint16_t* drow = p.D + static_cast<int64_t>(row) * p.N + static_cast<int64_t>(tn) * BN + half * kHalf;
+      // Drain this warp's part of the accumulator into registers as packed bf16, hand tensor memory
+      // back to the MMA warp, and only then write to global memory: the next tile's MMAs overlap
+      // the stores.
+      uint32_t packed[kHalf / 2];
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < kHalf; c0 += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * kHalf + c0, v);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 16; ++i)
@@ -503,23 +538,22 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        if constexpr (CG == 2) mbar_arrive_cluster(empty_target);
-        else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tmem_empty_bar) : "memory");
+        if (leader) mbar_arrive_local(tmem_empty_bar);
+        else mbar_arrive_cluster_relaxed(empty_target);
       }
       if (row < p.M) {
         uint4* dst = reinterpret_cast<uint4*>(drow);
 #pragma unroll
-        for (int i = 0; i < BN / 8; ++i)
+        for (int i = 0; i < kHalf / 8; ++i)
           dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
       }
       acc_phase ^= 1u;
-      if (prof) { t_body += clock64() - w1; ++n_tiles; }
+      if (eprof) { t_body += clock64() - w1; ++n_tiles; }
     }
-    if (prof) {
-      unsigned long long* c = reinterpret_cast<unsigned long long*>(p.status + 16);
-      c[6] = t_wait;
-      c[7] = t_body;
-      c[8] = n_tiles;
+    if (eprof) {
+      counters[6] = t_wait;
+      counters[7] = t_body;
+      counters[8] = n_tiles;
     }
   }
 
@@ -531,7 +565,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
   }
   if constexpr (CG == 2) cluster_sync_all();
-  if (warp == 1) {
+  if (warp == kWarpMma) {
     tc_fence_after();
     tmem_dealloc<CG>(tmem_base, kTmemCols);
   }
@@ -572,15 +606,14 @@ int encode_operand_map(CUtensorMap* map, const void* base, int rows, int k, int 
   return B2_OK;
 }
 
-// The swizzled scale buffer is [rows/128][K/64][512 bytes].  Viewed as uint16 with an extra
-// zero-stride dimension, (256, 4 replicas, K/64, rows/128), one load of box (256, 4, 4, chunks)
-// lands in shared memory as [chunk][k-block][replica][512 B].
+// The swizzled scale buffer is [rows/128][K/64][512 bytes]; viewed as uint16 (256, K/64, rows/128),
+// one load of box (256, 4, chunks) lands in shared memory as [chunk][k-block][512 B].
 int encode_scale_map(CUtensorMap* map, const void* base, int rows_padded, int k, int chunks) {
-  const cuuint64_t dims[4] = {256, 4, static_cast<cuuint64_t>(k / 64), static_cast<cuuint64_t>(rows_padded / 128)};
-  const cuuint64_t strides[3] = {0, 512, static_cast<cuuint64_t>(k) * 8};
-  const cuuint32_t box[4] = {256, 4, 4, static_cast<cuuint32_t>(chunks)};
-  const cuuint32_t elem[4] = {1, 1, 1, 1};
-  const CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims,
+  const cuuint64_t dims[3] = {256, static_cast<cuuint64_t>(k / 64), static_cast<cuuint64_t>(rows_padded / 128)};
+  const cuuint64_t strides[2] = {512, static_cast<cuuint64_t>(k) * 8};
+  const cuuint32_t box[3] = {256, 4, static_cast<cuuint32_t>(chunks)};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims,
                                        strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -619,7 +652,7 @@ struct MapSet {
 std::mutex g_mu;
 std::unordered_map<MapKey, MapSet, MapKeyHash> g_maps;
 uint32_t* g_status[64] = {nullptr};
-constexpr int kStatusWords = 64;  // 2 status words, padding, 9 64-bit role timers from word 16
+constexpr int kStatusWords = 64;  // 2 status words, padding, 12 64-bit role timers from word 16
 int g_profile = 0;
 
 
@@ -757,24 +790,25 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
     return B2_ERR_INVALID_ARGUMENT;
   }
   switch (variant) {
-    case 0: return launch_variant<1, 128, 4>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 0, s);
-    case 1: return launch_variant<1, 256, 3>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 1, s);
-    case 2: return launch_variant<2, 256, 4>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 2, s);
-    default: return launch_variant<2, 128, 5>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
+    case 0: return launch_variant<1, 128, 6>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 0, s);
+    case 1: return launch_variant<1, 256, 4>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 1, s);
+    case 2: return launch_variant<2, 256, 5>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 2, s);
+    default: return launch_variant<2, 128, 8>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
   }
 }
 
 // Role timers of CTA 0 for the most recent profiled launch (SM cycles): producer wait-for-free-stage,
 // producer total, MMA wait-for-data, MMA wait-for-accumulator, MMA total, MMA issue, epilogue
-// wait-for-accumulator, epilogue body, tiles.  `enable` switches recording for later launches.
-extern "C" int b2_nvfp4_gemm_role_timers(int enable, unsigned long long* out9, void* stream) {
+// wait-for-accumulator, epilogue body, tiles, scale-warp wait-for-load, scale-warp body, MMA total in nanoseconds.
+// `enable` switches recording for later launches.
+extern "C" int b2_nvfp4_gemm_role_timers(int enable, unsigned long long* out12, void* stream) {
   using namespace b2;
   uint32_t* status = nullptr;
   if (int rc = status_word(&status)) return rc;
   g_profile = enable ? 1 : 0;
-  if (out9) {
+  if (out12) {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    B2_CUDA_TRY(cudaMemcpyAsync(out9, status + 16, 9 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s));
+    B2_CUDA_TRY(cudaMemcpyAsync(out12, status + 16, 12 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s));
     B2_CUDA_TRY(cudaStreamSynchronize(s));
   }
   return B2_OK;
@@ -790,9 +824,14 @@ extern "C" int b2_nvfp4_gemm_status(void* stream) {
   B2_CUDA_TRY(cudaStreamSynchronize(s));
   if (host[0] == 0) return B2_OK;
   B2_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(host), s));
-  static const char* const kWhat[] = {"", "producer waiting for a free stage", "MMA waiting for a drained accumulator",
-                                      "MMA waiting for a loaded stage", "epilogue waiting for the accumulator"};
-  set_error("b2_nvfp4_gemm: bounded wait expired (%s) in CTA %u",
-            host[0] < 5 ? kWhat[host[0]] : "unknown", host[1]);
+  static const char* const kWhat[] = {"",
+                                      "producer waiting for a free stage",
+                                      "MMA waiting for a drained accumulator",
+                                      "MMA waiting for loaded operands",
+                                      "epilogue waiting for the accumulator",
+                                      "scale warp waiting for loaded scale factors",
+                                      "MMA waiting for scale factors in tensor memory"};
+  set_error("b2_nvfp4_gemm: bounded wait expired (%s) in CTA %u", host[0] < 7 ? kWhat[host[0]] : "unknown",
+            host[1]);
   return B2_ERR_DEVICE_TIMEOUT;
 }

@@ -58,17 +58,21 @@ __device__ __forceinline__ void quantize_block(const uint32_t (&w)[8], float gs,
   // out_scale = rcp(sf * rcp(gs)), zero when the stored scale is zero.
   const float inv = rcp_approx_ftz(mul_f32(sf_f32, rcp_gs));
   const float out_scale = (sf_f32 == 0.0f) ? 0.0f : inv;
+  // x * out_scale, two elements per mul.f32x2 (each half rounds like mul.f32)
+  const float2 s2 = make_float2(out_scale, out_scale);
   float v[8];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    v[2 * i] = mul_f32(unpack_lo<Tag>(w[i]), out_scale);
-    v[2 * i + 1] = mul_f32(unpack_hi<Tag>(w[i]), out_scale);
+    const float2 q = mul_f32x2(unpack2<Tag>(w[i]), s2);
+    v[2 * i] = q.x;
+    v[2 * i + 1] = q.y;
   }
   packed.x = cvt_e2m1x8(v);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    v[2 * i] = mul_f32(unpack_lo<Tag>(w[4 + i]), out_scale);
-    v[2 * i + 1] = mul_f32(unpack_hi<Tag>(w[4 + i]), out_scale);
+    const float2 q = mul_f32x2(unpack2<Tag>(w[4 + i]), s2);
+    v[2 * i] = q.x;
+    v[2 * i + 1] = q.y;
   }
   packed.y = cvt_e2m1x8(v);
 }

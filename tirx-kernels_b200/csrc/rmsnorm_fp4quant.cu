@@ -7,9 +7,12 @@
 // one; partial sums are combined by an XOR butterfly inside the warp and, for rows
 // wider than a warp, by a second butterfly over the per-warp partials.  This kernel
 // keeps that tree and changes the data movement: the row is read from HBM exactly
-// once with 128-bit loads, parked in shared memory, and the quantization pass reads
-// it back from there; each thread quantizes 8 values (block amax by a 2- or 4-lane
-// shuffle) so packed output is written as fully coalesced 32-bit words.
+// once with 128-bit loads and parked in shared memory; the quantization pass reads it
+// back from there with one thread per scale block (no shuffles, the scale computed
+// once per block) and writes packed output as coalesced 64-bit words.  The kernel is
+// bound by instruction issue as much as by HBM, so squares are accumulated with FMA
+// (bit-identical here, the squares being exact in fp32) and the scaling multiplies
+// use the two-wide mul.f32x2.
 #include <algorithm>
 
 #include "common.cuh"
@@ -51,26 +54,43 @@ __device__ __forceinline__ float ue8m0_to_output_scale(uint32_t code) {
   return code == 0u ? 0.0f : cand;
 }
 
+// acc + x*x for eight values in element order.  The square of a bf16/fp16 value is exact in fp32,
+// so one FMA per element rounds exactly like the reference's mul.f32 followed by add.f32.
 template <typename Tag>
 __device__ __forceinline__ float sum_sq_8(float acc, const uint4& c) {
   const uint32_t w[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const float lo = unpack_lo<Tag>(w[i]), hi = unpack_hi<Tag>(w[i]);
-    acc = add_f32(acc, mul_f32(lo, lo));
-    acc = add_f32(acc, mul_f32(hi, hi));
+    acc = __fmaf_rn(lo, lo, acc);
+    acc = __fmaf_rn(hi, hi, acc);
   }
   return acc;
 }
 
-template <typename Tag, int TPR>
+// Eight products p (packed pairs) -> eight E2M1 nibbles of (p * rstd) * out_scale.
+template <typename Tag>
+__device__ __forceinline__ uint32_t quantize_8(const uint32_t (&prod)[4], float rstd, float out_scale) {
+  const float2 r2 = make_float2(rstd, rstd), o2 = make_float2(out_scale, out_scale);
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 q = mul_f32x2(mul_f32x2(unpack2<Tag>(prod[i]), r2), o2);
+    v[2 * i] = q.x;
+    v[2 * i + 1] = q.y;
+  }
+  return cvt_e2m1x8(v);
+}
+
+template <typename Tag, int TPR, int BLOCK>
 __global__ void __launch_bounds__(TPR == 256 ? 256 : 128)
     rmsnorm_fp4quant_kernel(const __grid_constant__ RmsParams p) {
   constexpr int kThreads = TPR == 256 ? 256 : 128;
   constexpr int kRows = kThreads / TPR;
   constexpr int kWarpsPerRow = TPR >= 32 ? TPR / 32 : 1;
+  constexpr int kChunksPerBlock = BLOCK / 8;  // 16-byte chunks per scale block
   extern __shared__ __align__(16) uint8_t smem[];
-  uint4* tile = reinterpret_cast<uint4*>(smem);  // [kRows][vb][TPR] chunks of 8 values
+  uint4* tile = reinterpret_cast<uint4*>(smem);  // [kRows][vb * TPR] chunks of 8 values, row-contiguous
   float* red = reinterpret_cast<float*>(smem + static_cast<size_t>(kRows) * p.vb * TPR * 16);
 
   const int tid = threadIdx.x;
@@ -86,9 +106,9 @@ __global__ void __launch_bounds__(TPR == 256 ? 256 : 128)
 
   const float rcp6 = rcp_approx_ftz(6.0f);
   const uint4* xrow = reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(row) * p.H * 2);
-  uint4* my_tile = tile + static_cast<size_t>(row_in_cta) * p.vb * TPR + t;
+  uint4* my_row = tile + static_cast<size_t>(row_in_cta) * p.vb * TPR;
 
-  // ---- pass 1: one HBM read of the row, squares accumulated in chunk order -------------
+  // ---- pass 1: one HBM read of the row; virtual thread t adds chunks t, t+TPR, ... in order ----
   float sum = 0.0f;
   for (int b0 = 0; b0 < p.vb; b0 += 4) {
     uint4 c[4];
@@ -106,7 +126,7 @@ __global__ void __launch_bounds__(TPR == 256 ? 256 : 128)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       if (ok[j]) {
-        my_tile[(b0 + j) * TPR] = c[j];
+        my_row[t + (b0 + j) * TPR] = c[j];
         sum = sum_sq_8<Tag>(sum, c[j]);
       }
     }
@@ -124,34 +144,36 @@ __global__ void __launch_bounds__(TPR == 256 ? 256 : 128)
 #pragma unroll
     for (int x = 1; x < 32; x <<= 1) part = add_f32(part, __shfl_xor_sync(0xFFFFFFFFu, part, x));
     sum = part;
+  } else {
+    __syncthreads();  // pass 2 reads chunks other threads of the row parked
   }
   const float shifted =
       p.pow2 ? __fmaf_rn(sum, p.inv_h, p.eps) : add_f32(__fdiv_rn(sum, static_cast<float>(p.H)), p.eps);
   const float rstd = rsqrt_approx_ftz(shifted);
   const float gs = p.use_e4m3 ? *p.gs : 0.0f;
+  if (!row_valid) return;
 
-  // ---- pass 2: scale, quantize and pack from the shared-memory copy ---------------------
+  // ---- pass 2: one thread per scale block, from the shared-memory copy ----
   const uint4* wrow = reinterpret_cast<const uint4*>(p.w);
-  const int group = p.block_size >> 3;  // lanes sharing one scale factor: 2 or 4
   uint8_t* yrow = p.y + static_cast<int64_t>(row) * (p.H >> 1);
-  for (int b = 0; b < p.vb; ++b) {
-    const int chunk = t + b * TPR;
-    const bool ok = row_valid && chunk < nchunks;
-    uint32_t prod[4] = {0u, 0u, 0u, 0u};
-    if (ok) {
-      const uint4 xc = my_tile[b * TPR];
-      const uint4 wc = __ldg(wrow + chunk);
-      prod[0] = hmul2<Tag>(xc.x, wc.x);
-      prod[1] = hmul2<Tag>(xc.y, wc.y);
-      prod[2] = hmul2<Tag>(xc.z, wc.z);
-      prod[3] = hmul2<Tag>(xc.w, wc.w);
+  // byte offset of scale (row, 0); scale (row, j) lives at + j (linear) or + (j >> 2) * 512 + (j & 3)
+  const int64_t sf_row = p.swizzled ? sf_offset_128x4(row, 0, p.sf_pad_cols) : static_cast<int64_t>(row) * p.sf_cols;
+  uint8_t* sf_base = p.sf + sf_row;
+  for (int j = t; j < p.sf_cols; j += TPR) {
+    uint32_t prod[kChunksPerBlock][4];
+#pragma unroll
+    for (int c = 0; c < kChunksPerBlock; ++c) {
+      const uint4 xc = my_row[j * kChunksPerBlock + c];
+      const uint4 wc = __ldg(wrow + j * kChunksPerBlock + c);
+      prod[c][0] = hmul2<Tag>(xc.x, wc.x);
+      prod[c][1] = hmul2<Tag>(xc.y, wc.y);
+      prod[c][2] = hmul2<Tag>(xc.z, wc.z);
+      prod[c][3] = hmul2<Tag>(xc.w, wc.w);
     }
-    float amax = pair_max_to_f32<Tag>(absmax_4<Tag>(prod));
-    amax = max_f32(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-    if (group == 4) amax = max_f32(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-    if (!ok) continue;
-
-    const float max_abs = mul_f32(amax, rstd);
+    uint32_t m2 = absmax_4<Tag>(prod[0]);
+#pragma unroll
+    for (int c = 1; c < kChunksPerBlock; ++c) m2 = hmax2<Tag>(m2, absmax_4<Tag>(prod[c]));
+    const float max_abs = mul_f32(pair_max_to_f32<Tag>(m2), rstd);
     uint32_t code;
     float out_scale;
     if (p.use_e4m3) {
@@ -164,19 +186,15 @@ __global__ void __launch_bounds__(TPR == 256 ? 256 : 128)
       code = cvt_f32_to_ue8m0(mul_f32(max_abs, rcp6));
       out_scale = ue8m0_to_output_scale(code);
     }
-    float v[8];
+    uint32_t q[kChunksPerBlock];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      v[2 * i] = mul_f32(mul_f32(unpack_lo<Tag>(prod[i]), rstd), out_scale);
-      v[2 * i + 1] = mul_f32(mul_f32(unpack_hi<Tag>(prod[i]), rstd), out_scale);
+    for (int c = 0; c < kChunksPerBlock; ++c) q[c] = quantize_8<Tag>(prod[c], rstd, out_scale);
+    if constexpr (kChunksPerBlock == 2) {
+      *reinterpret_cast<uint2*>(yrow + j * 8) = make_uint2(q[0], q[1]);
+    } else {
+      *reinterpret_cast<uint4*>(yrow + j * 16) = make_uint4(q[0], q[1], q[2], q[3]);
     }
-    *reinterpret_cast<uint32_t*>(yrow + chunk * 4) = cvt_e2m1x8(v);
-    if ((chunk & (group - 1)) == 0) {
-      const int sf_index = chunk / group;
-      const int64_t off = p.swizzled ? sf_offset_128x4(row, sf_index, p.sf_pad_cols)
-                                     : static_cast<int64_t>(row) * p.sf_cols + sf_index;
-      p.sf[off] = static_cast<uint8_t>(code);
-    }
+    sf_base[p.swizzled ? ((j >> 2) * 512 + (j & 3)) : j] = static_cast<uint8_t>(code);
   }
   if (p.enable_pdl) pdl_launch_dependents();
 }
@@ -191,12 +209,12 @@ int threads_per_row(int h) {
   return 256;
 }
 
-template <typename Tag, int TPR>
+template <typename Tag, int TPR, int BLOCK>
 int launch(const RmsParams& p, cudaStream_t stream) {
   constexpr int kThreads = TPR == 256 ? 256 : 128;
   constexpr int kRows = kThreads / TPR;
   constexpr int kWarpsPerRow = TPR >= 32 ? TPR / 32 : 1;
-  auto kernel = rmsnorm_fp4quant_kernel<Tag, TPR>;
+  auto kernel = rmsnorm_fp4quant_kernel<Tag, TPR, BLOCK>;
   const size_t smem = static_cast<size_t>(kRows) * p.vb * TPR * 16 + kRows * kWarpsPerRow * 4;
   if (smem > 48 * 1024) {
     B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -218,16 +236,21 @@ int launch(const RmsParams& p, cudaStream_t stream) {
   return B2_OK;
 }
 
-template <typename Tag>
+template <typename Tag, int BLOCK>
 int dispatch_tpr(const RmsParams& p, int tpr, cudaStream_t stream) {
   switch (tpr) {
-    case 8: return launch<Tag, 8>(p, stream);
-    case 16: return launch<Tag, 16>(p, stream);
-    case 32: return launch<Tag, 32>(p, stream);
-    case 64: return launch<Tag, 64>(p, stream);
-    case 128: return launch<Tag, 128>(p, stream);
-    default: return launch<Tag, 256>(p, stream);
+    case 8: return launch<Tag, 8, BLOCK>(p, stream);
+    case 16: return launch<Tag, 16, BLOCK>(p, stream);
+    case 32: return launch<Tag, 32, BLOCK>(p, stream);
+    case 64: return launch<Tag, 64, BLOCK>(p, stream);
+    case 128: return launch<Tag, 128, BLOCK>(p, stream);
+    default: return launch<Tag, 256, BLOCK>(p, stream);
   }
+}
+
+template <typename Tag>
+int dispatch_block(const RmsParams& p, int tpr, cudaStream_t stream) {
+  return p.block_size == 16 ? dispatch_tpr<Tag, 16>(p, tpr, stream) : dispatch_tpr<Tag, 32>(p, tpr, stream);
 }
 
 }  // namespace
@@ -295,6 +318,6 @@ extern "C" int b2_rmsnorm_fp4quant(const void* x, const void* w, void* y, void* 
     return B2_ERR_UNSUPPORTED;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (in_dtype == B2_DTYPE_F16) return dispatch_tpr<F16Tag>(p, tpr, s);
-  return dispatch_tpr<BF16Tag>(p, tpr, s);
+  if (in_dtype == B2_DTYPE_F16) return dispatch_block<F16Tag>(p, tpr, s);
+  return dispatch_block<BF16Tag>(p, tpr, s);
 }
