@@ -119,6 +119,17 @@ int b2_nvfp4_gemm_set_variant(int variant);
 int b2_nvfp4_gemm_status(void* stream);
 
 /*
+ * In-kernel role timers of b2_nvfp4_gemm (observability; the reference's nearest analogue is the
+ * u64 event buffer of tirx_kernels/basic/allgather_gemm.py:48-53).  `enable` != 0 makes later
+ * launches record, for CTA 0, SM-cycle counters per warp role; `out12` (host, may be NULL)
+ * receives the counters of the last recorded launch: [0] operand producer waiting for a free
+ * stage, [1] producer total, [2] MMA waiting for data, [3] MMA waiting for a drained accumulator,
+ * [4] MMA total, [5] MMA issue, [6] epilogue waiting, [7] epilogue body, [8] tiles,
+ * [9] scale warp waiting, [10] scale warp body, [11] MMA total in nanoseconds.
+ */
+int b2_nvfp4_gemm_role_timers(int enable, unsigned long long* out12, void* stream);
+
+/*
  * cuBLASLt NVFP4 matmul, the library peer the reference times beside its own
  * kernel: nvfp4_cublaslt in tirx_kernels/basic/nvfp4_gemm.py:196-239.
  * Lives in a separate shared object (libb200nvfp4_cublaslt.so) so the product

@@ -73,10 +73,6 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
-               : "memory");
-}
 // Remote arrive without memory ordering: for hand-offs whose payload lives in tensor memory and
 // has already been completed with tcgen05.wait, so no generic-proxy writes need publishing.
 __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_bar) {

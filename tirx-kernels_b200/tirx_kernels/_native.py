@@ -33,6 +33,7 @@ MAIN_SIGNATURES = {
     "b2_nvfp4_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "b2_nvfp4_gemm_status": (_i, [_vp]),
     "b2_nvfp4_gemm_set_variant": (_i, [_i]),
+    "b2_nvfp4_gemm_role_timers": (_i, [_i, _vp, _vp]),
     "b2_mufu_probe": (_i, [_i, _vp, _vp, _i, _vp]),
 }
 CUBLASLT_SIGNATURES = {
@@ -77,8 +78,27 @@ def lib() -> ctypes.CDLL:
 def cublaslt_lib() -> ctypes.CDLL:
     global _CUBLASLT
     if _CUBLASLT is None:
+        _preload_torch_cublaslt()
         _CUBLASLT = _load("libb200nvfp4_cublaslt.so", CUBLASLT_SIGNATURES)
     return _CUBLASLT
+
+
+def _preload_torch_cublaslt() -> None:
+    """Load the cuBLASLt build PyTorch ships before ours resolves its `libcublasLt.so.12`.
+
+    PyTorch links against its own cuBLAS / cuBLASLt pair; if a different cuBLASLt with the same
+    soname is mapped first, torch's cuBLAS later binds to it and fails with INVALID_VALUE.
+    """
+    try:
+        import nvidia.cublas as _pkg
+
+        for root in _pkg.__path__:
+            candidate = Path(root) / "lib" / "libcublasLt.so.12"
+            if candidate.exists():
+                ctypes.CDLL(str(candidate), mode=ctypes.RTLD_GLOBAL)
+                return
+    except ImportError:
+        pass
 
 
 def last_error() -> str:
