@@ -47,58 +47,66 @@ def rank_env() -> tuple[int, int, int]:
 
 # ---- clocks -------------------------------------------------------------------------------------
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples the SM clock and throttle reasons of one GPU (NVML, every 10 ms) while a region runs."""
 
-    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._pump, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            physical = int(visible.split(",")[self.index]) if visible and visible.split(",")[self.index].isdigit() \
+                else self.index
+            self._nvml, self._handle = pynvml, pynvml.nvmlDeviceGetHandleByIndex(physical)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            self._thread = threading.Thread(target=self._pump, daemon=True)
+            self._thread.start()
+        except Exception:
+            self._thread = None
         return self
 
     def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+                for name, bit in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                break
+            time.sleep(0.01)
 
     def __exit__(self, *exc):
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=5)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
 
     def summary(self) -> dict:
-        clocks, maxes, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                clocks.append(float(parts[0]))
-                maxes.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, flag in zip(names, parts[3:7]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        if not clocks:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        busy = [c for c in clocks if c > 0.5 * max(clocks)] or clocks
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(maxes), "reasons": sorted(reasons),
-                "samples": len(clocks)}
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        busy = [c for c in self.samples if c > 0.5 * max(self.samples)] or self.samples
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def keep_busy(fn, seconds: float) -> None:
+    """Runs `fn` back to back for about `seconds` so that clock samples are taken under load."""
+    import torch
+
+    end = time.perf_counter() + seconds
+    while time.perf_counter() < end:
+        for _ in range(20):
+            fn()
+        torch.cuda.synchronize()
 
 
 # ---- data -----------------------------------------------------------------------------------------
@@ -163,8 +171,12 @@ def run_ours(args) -> dict:
     def step():
         quant._run_launch(ex, x, gs, out, sf, m, k, layout)
 
+    # the clock sampler runs from a short busy period before the timed region to one after it, so
+    # that its samples describe the GPU under this very load even when the region lasts milliseconds
     with ClockSampler(local_rank) as sampler:
+        keep_busy(step, 0.3)
         elapsed_ms = timed_region(step, args.steps, args.warmup, distributed)
+        keep_busy(step, 0.15)
     clocks = sampler.summary()
     ms_per_step = elapsed_ms / args.steps
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
@@ -302,7 +314,7 @@ def extras(args, rank: int, world: int, distributed: bool) -> dict:
             entry = {"us": us, "tflops": gemm.flops(M, N, K) / us / 1e6}
             entry["roofline"] = (_checks.roofline_nvfp4(gemm.flops(M, N, K), us) if M > 16
                                  else _checks.roofline_hbm(gemm.algorithmic_bytes(M, N, K), us))
-            if M > 16 and args.with_cublaslt:
+            if M > 16 and not args.no_cublaslt:
                 try:
                     D2 = torch.empty_like(D)
                     lt = lambda: _native.nvfp4_gemm_cublaslt(A_fp4, B_fp4, A_sf, B_sf, float(alpha), D2, M, N, K)
@@ -326,7 +338,10 @@ def ffn_sharded(rank: int, world: int, distributed: bool, M: int = 8192, N: int 
     from tirx_kernels import _checks, _native
     from tirx_kernels.basic import nvfp4_gemm as gemm
 
-    shard = N // world
+    from tirx_kernels.basic import ffn_tp
+
+    start, stop = ffn_tp.shard_rows(N, world, rank)
+    shard = stop - start
     g = torch.Generator(device="cuda").manual_seed(1000 + rank)
     act = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, generator=torch.Generator(device="cuda").manual_seed(0))
     w = (0.02 * torch.randn(shard, K, device="cuda", dtype=torch.float32, generator=g)).to(torch.bfloat16)
@@ -344,20 +359,22 @@ def ffn_sharded(rank: int, world: int, distributed: bool, M: int = 8192, N: int 
     gathered = torch.empty(world, M, shard, dtype=torch.bfloat16, device="cuda") if distributed else None
     exg = gemm._compile_executable(M, shard, K)
 
-    def quantize():
-        _native.nvfp4_quantize(act, A_fp4, A_sf, a_gs, M, K, "bfloat16", "128x4")
+    def quantize(x=act):
+        _native.nvfp4_quantize(x, A_fp4, A_sf, a_gs, M, K, "bfloat16", "128x4")
+        return A_fp4, A_sf
 
-    def matmul():
-        exg(A_fp4, B_fp4, A_sf, B_sf, alpha_t, D)
+    def matmul(a=A_fp4, a_sf=A_sf, b=B_fp4, b_sf=B_sf, al=alpha_t, out=D):
+        exg(a, b, a_sf, b_sf, al, out)
 
     def gather():
         if distributed:
             torch.distributed.all_gather_into_tensor(gathered.view(-1), D.view(-1))
 
+    projection = ffn_tp.ShardedProjection(world, rank, M, N, K, B_fp4, B_sf, alpha_t, quantize,
+                                          lambda a, a_sf, b, b_sf, al, out: exg(a, b, a_sf, b_sf, al, out))
+
     def whole():
-        quantize()
-        matmul()
-        gather()
+        projection.forward(act, D, gathered)
 
     def phase_us(fn, reps=10):
         ms = timed_region(fn, reps, 3, distributed)
@@ -412,7 +429,7 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-extra", action="store_true", help="headline only")
-    parser.add_argument("--with-cublaslt", action="store_true", help="also time the cuBLASLt NVFP4 matmul")
+    parser.add_argument("--no-cublaslt", action="store_true", help="do not time the cuBLASLt NVFP4 peer")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
     line = run_reference(args) if args.impl == "reference" else run_ours(args)

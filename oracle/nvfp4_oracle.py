@@ -510,3 +510,86 @@ def rmsnorm_reference_f32(x_bits, w_bits, dtype: str, eps: float) -> np.ndarray:
     w = bits_to_f32(w_bits, dtype).astype(np.float32)
     normalized = x * (1.0 / np.sqrt((x * x).mean(axis=-1, keepdims=True) + np.float32(eps)))
     return bits_to_f32(f32_to_bits((normalized * w).astype(np.float32), dtype), dtype)
+
+
+# --------------------------------------------------------------------------------------
+# recorded MUFU values: lets a machine without a GPU replay what the hardware returned
+# --------------------------------------------------------------------------------------
+MUFU_OPS = ("rcp_ftz", "rsqrt_ftz", "lg2", "ex2", "ex2_ftz")
+
+
+class RecordingMufu:
+    """Wraps a provider and remembers every (op, input bits) -> output bits pair it served."""
+
+    name = "recording"
+
+    def __init__(self, inner):
+        self._inner = inner
+        self.tables = {op: {} for op in MUFU_OPS}
+
+    def _wrap(self, op, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.asarray(getattr(self._inner, op)(x), dtype=np.float32)
+        keys = x.reshape(-1).view(np.uint32)
+        vals = out.reshape(-1).view(np.uint32)
+        uniq, first = np.unique(keys, return_index=True)
+        self.tables[op].update(zip(uniq.tolist(), vals[first].tolist()))
+        return out
+
+    def rcp_ftz(self, x):
+        return self._wrap("rcp_ftz", x)
+
+    def rsqrt_ftz(self, x):
+        return self._wrap("rsqrt_ftz", x)
+
+    def lg2(self, x):
+        return self._wrap("lg2", x)
+
+    def ex2(self, x):
+        return self._wrap("ex2", x)
+
+    def ex2_ftz(self, x):
+        return self._wrap("ex2_ftz", x)
+
+    def arrays(self) -> dict:
+        out = {}
+        for op, table in self.tables.items():
+            keys = np.array(sorted(table), dtype=np.uint32)
+            out[f"{op}_in"] = keys
+            out[f"{op}_out"] = np.array([table[k] for k in keys.tolist()], dtype=np.uint32)
+        return out
+
+
+class TableMufu:
+    """Replays recorded hardware values; an input that was never recorded is an error."""
+
+    name = "table"
+
+    def __init__(self, arrays):
+        self._tables = {op: (np.asarray(arrays[f"{op}_in"], dtype=np.uint32),
+                             np.asarray(arrays[f"{op}_out"], dtype=np.uint32)) for op in MUFU_OPS}
+
+    def _lookup(self, op, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        keys, vals = self._tables[op]
+        bits = x.reshape(-1).view(np.uint32)
+        pos = np.searchsorted(keys, bits)
+        pos = np.minimum(pos, max(len(keys) - 1, 0))
+        if len(keys) == 0 or not np.array_equal(keys[pos], bits):
+            raise KeyError(f"{op}: input not in the recorded table")
+        return vals[pos].view(np.float32).reshape(x.shape)
+
+    def rcp_ftz(self, x):
+        return self._lookup("rcp_ftz", x)
+
+    def rsqrt_ftz(self, x):
+        return self._lookup("rsqrt_ftz", x)
+
+    def lg2(self, x):
+        return self._lookup("lg2", x)
+
+    def ex2(self, x):
+        return self._lookup("ex2", x)
+
+    def ex2_ftz(self, x):
+        return self._lookup("ex2_ftz", x)

@@ -1,0 +1,82 @@
+"""Pins the CPU oracle against golden vectors produced by flashinfer's own GPU kernels.
+
+The reference's tests compare with flashinfer at run time and store nothing; the fixtures under
+tests/golden/ were produced on a B200 by tests/golden/make_flashinfer_golden.py (flashinfer
+0.6.11, both its CUDA and CuTe-DSL back-ends agreed on every case).  The hardware-approximate
+instruction values the oracle needs were recorded in the same run and are replayed here, so the
+comparison is bit for bit without a GPU.
+"""
+
+import importlib.util
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import c_oracle
+from oracle import nvfp4_oracle as o
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+MANIFEST = json.loads((GOLDEN / "MANIFEST.json").read_text())
+
+
+def _generator():
+    spec = importlib.util.spec_from_file_location("make_flashinfer_golden", GOLDEN / "make_flashinfer_golden.py")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module
+
+
+GEN = _generator()
+TABLE = o.TableMufu(np.load(GOLDEN / "mufu_tables.npz"))
+CASES = {c["name"]: c for c in MANIFEST["cases"] if c["status"] == "ok"}
+
+
+def test_manifest_is_complete():
+    assert len(CASES) == len(GEN.QUANT_CASES) + len(GEN.RMS_CASES)
+    assert MANIFEST["mufu_tables"] == "ok"
+    assert all(c.get("cuda_backend_identical", True) for c in CASES.values())
+
+
+@pytest.mark.parametrize("index", range(len(GEN.QUANT_CASES)))
+def test_quantizer_oracle_matches_flashinfer_bytes(index):
+    case = GEN.QUANT_CASES[index]
+    entry, gold = CASES[f"quant_{index}"], np.load(GOLDEN / f"quant_{index}.npz")
+    a, gs = GEN.quant_inputs(case)
+    assert GEN.digest(GEN.bits(a), np.float32(gs)) == entry["input_sha256"], "seeded input drifted"
+    dtype, m, k, layout, _ = case
+    for impl in (o.nvfp4_quantize, c_oracle.nvfp4_quantize):
+        packed, sf = impl(GEN.bits(a), dtype, gs, layout, mufu=TABLE)
+        assert np.array_equal(packed.reshape(-1), gold["packed"].reshape(-1))
+        assert np.array_equal(sf, gold["sf"][: sf.size])
+
+
+@pytest.mark.parametrize("index", range(len(GEN.RMS_CASES)))
+def test_rmsnorm_oracle_matches_flashinfer_bytes(index):
+    case = GEN.RMS_CASES[index]
+    entry, gold = CASES[f"rms_{index}"], np.load(GOLDEN / f"rms_{index}.npz")
+    x, w, gs = GEN.rms_inputs(case)
+    assert GEN.digest(GEN.bits(x), GEN.bits(w), np.float32(gs)) == entry["input_sha256"], "seeded input drifted"
+    dtype, M, H, block, fmt, swizzled, _ = case
+    packed, sf = o.rmsnorm_fp4quant(GEN.bits(x), GEN.bits(w), dtype, gs, 1e-6, block, fmt, swizzled, TABLE)
+    assert np.array_equal(packed.reshape(-1), gold["packed"].reshape(-1))
+    layout = "128x4" if swizzled else "linear"
+    mine = o.logical_scales(sf, M, H // block, layout)
+    theirs = o.logical_scales(gold["sf"], M, H // block, layout)
+    assert np.array_equal(mine, theirs)
+    if block == 16:
+        packed_c, sf_c = c_oracle.rmsnorm_fp4quant(GEN.bits(x), GEN.bits(w), dtype, gs, 1e-6, swizzled, TABLE)
+        assert np.array_equal(packed_c, packed)
+        assert np.array_equal(o.logical_scales(sf_c, M, H // block, layout), mine)
+
+
+def test_exact_rounding_is_not_what_the_hardware_does():
+    """Documents why the table exists: correctly rounded reciprocals differ from the B200's in some inputs."""
+    arrays = np.load(GOLDEN / "mufu_tables.npz")
+    x = arrays["rcp_ftz_in"].view(np.float32)
+    hw = arrays["rcp_ftz_out"].view(np.float32)
+    exact = o.ExactMufu().rcp_ftz(x)
+    ulps = np.abs(hw.view(np.int32).astype(np.int64) - exact.view(np.int32).astype(np.int64))
+    assert ulps.max() <= 1
+    assert hw[np.flatnonzero(x == np.float32(6.0))[0]].view(np.uint32) == 0x3E2AAAAB
