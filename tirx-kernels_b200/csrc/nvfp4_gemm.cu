@@ -43,6 +43,8 @@ struct GemmParams {
   uint32_t* status;  // [0]: first failure code, [1]: detail; role timers from byte 64 on
   int profile;       // CTA 0 records per-role cycle counters when set
   int M, N, K;
+  int splits;        // K is cut into `splits` ranges, each its own work item (1 = no split)
+  float* partial;    // [splits][M][N] fp32 partial sums when splits > 1
   int tiles_m, tiles_n;  // in units of (cta_group * 128) rows and BN columns
   int group_n;           // tile-order grouping along N
 };
@@ -335,8 +337,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const bool leader = rank == 0;
   const int unit = CG == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int num_units = CG == 2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-  const int num_tiles = p.tiles_m * p.tiles_n;
-  const int k_slabs = p.K / kBlockK;
+  const int num_tiles = p.tiles_m * p.tiles_n * p.splits;  // work items: (tile, K range)
+  const int k_slabs = p.K / kBlockK / p.splits;            // slabs per work item
   const bool prof = p.profile && blockIdx.x == 0 && lane == 0;
   unsigned long long* counters = reinterpret_cast<unsigned long long*>(p.status + 16);
 
@@ -375,10 +377,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       long long t_wait = 0, t_begin = prof ? clock64() : 0;
       for (int t = unit; t < num_tiles && alive; t += num_units) {
         int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
+        tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
         const int row_a = (tm * CG + static_cast<int>(rank)) * kBlockM;
         const int row_b = tn * BN + static_cast<int>(rank) * L::kBRows;
-        for (int ks = 0; ks < k_slabs; ++ks) {
+        const int k_first = (t % p.splits) * k_slabs;
+        for (int ks = k_first; ks < k_first + k_slabs; ++ks) {
           const long long w0 = prof ? clock64() : 0;
           if (!wait_or_abort(empty_bar(stage), phase ^ 1u, ctx, 1u)) { alive = false; break; }
           if (prof) t_wait += clock64() - w0;
@@ -509,7 +512,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     long long t_wait = 0, t_body = 0, n_tiles = 0;
     for (int t = unit; t < num_tiles; t += num_units) {
       int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
+      tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
       const long long w0 = eprof ? clock64() : 0;
       if (!wait_or_abort(tmem_full_bar, acc_phase, ctx, 4u)) break;
       const long long w1 = eprof ? clock64() : 0;
@@ -520,6 +523,31 @@ __global__ void __launch_bounds__(kThreads, 1)
       // Drain this warp's part of the accumulator into registers as packed bf16, hand tensor memory
       // back to the MMA warp, and only then write to global memory: the next tile's MMAs overlap
       // the stores.
+      if (p.splits > 1) {
+        // split K: this work item's fp32 partial sums go to scratch; a second kernel adds the ranges
+        float* prow = p.partial + (static_cast<int64_t>(t % p.splits) * p.M + row) * p.N +
+                      static_cast<int64_t>(tn) * BN + half * kHalf;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kHalf; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * kHalf + c0, v);
+          tmem_ld_wait();
+          if (row < p.M) {
+            uint4* dst = reinterpret_cast<uint4*>(prow + c0);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive_local(tmem_empty_bar);
+          else mbar_arrive_cluster_relaxed(empty_target);
+        }
+        acc_phase ^= 1u;
+        if (eprof) { t_body += clock64() - w1; ++n_tiles; }
+        continue;
+      }
       uint32_t packed[kHalf / 2];
 #pragma unroll
       for (int c0 = 0; c0 < kHalf; c0 += 32) {
@@ -671,32 +699,47 @@ int status_word(uint32_t** out) {
   return B2_OK;
 }
 
+// D = bf16(alpha * sum over K ranges of the fp32 partial sums), ranges added in index order.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ alpha,
+                                     uint16_t* __restrict__ D, int64_t mn, int splits) {
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (i >= mn) return;
+  float acc[8];
+  {
+    const float4 a = *reinterpret_cast<const float4*>(partial + i), b = *reinterpret_cast<const float4*>(partial + i + 4);
+    acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w; acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
+  }
+  for (int s = 1; s < splits; ++s) {
+    const float* src = partial + s * mn + i;
+    const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+  }
+  const float al = __ldg(alpha);
+  uint4 out;
+  out.x = pack_from_f32<BF16Tag>(acc[0] * al, acc[1] * al);
+  out.y = pack_from_f32<BF16Tag>(acc[2] * al, acc[3] * al);
+  out.z = pack_from_f32<BF16Tag>(acc[4] * al, acc[5] * al);
+  out.w = pack_from_f32<BF16Tag>(acc[6] * al, acc[7] * al);
+  *reinterpret_cast<uint4*>(D + i) = out;
+}
+
 template <int CG, int BN, int STAGES>
-int launch_variant(const void* A, const void* B, const void* SFA, const void* SFB, const float* alpha,
-                   void* D, int M, int N, int K, int variant, cudaStream_t stream) {
+int encode_maps(MapSet* maps, const void* A, const void* B, const void* SFA, const void* SFB, int M, int N, int K) {
+  using L = SmemLayout<CG, BN, STAGES>;
+  const int m_padded = (M + 127) / 128 * 128, n_padded = (N + 127) / 128 * 128;
+  if (int rc = encode_operand_map(&maps->a, A, M, K, kBlockM)) return rc;
+  if (int rc = encode_operand_map(&maps->b, B, N, K, L::kBRows)) return rc;
+  if (int rc = encode_scale_map(&maps->sfa, SFA, m_padded, K, 1)) return rc;
+  if (int rc = encode_scale_map(&maps->sfb, SFB, n_padded, K, L::kChunks)) return rc;
+  return B2_OK;
+}
+
+// Launches the GEMM (and, with splits > 1, the reduction) on prepared tensor maps and scratch.
+template <int CG, int BN, int STAGES>
+int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N, int K, int splits,
+                   uint32_t* status, float* partial, cudaStream_t stream) {
   using L = SmemLayout<CG, BN, STAGES>;
   auto kernel = nvfp4_gemm_kernel<CG, BN, STAGES>;
-  uint32_t* status = nullptr;
-  if (int rc = status_word(&status)) return rc;
-
-  MapSet maps;
-  {
-    const MapKey key{A, B, SFA, SFB, M, N, K, variant};
-    std::lock_guard<std::mutex> lock(g_mu);
-    auto it = g_maps.find(key);
-    if (it == g_maps.end()) {
-      MapSet fresh;
-      const int m_padded = (M + 127) / 128 * 128, n_padded = (N + 127) / 128 * 128;
-      if (int rc = encode_operand_map(&fresh.a, A, M, K, kBlockM)) return rc;
-      if (int rc = encode_operand_map(&fresh.b, B, N, K, L::kBRows)) return rc;
-      if (int rc = encode_scale_map(&fresh.sfa, SFA, m_padded, K, 1)) return rc;
-      if (int rc = encode_scale_map(&fresh.sfb, SFB, n_padded, K, L::kChunks)) return rc;
-      if (g_maps.size() > 4096) g_maps.clear();
-      it = g_maps.emplace(key, fresh).first;
-    }
-    maps = it->second;
-  }
-
   GemmParams p;
   p.alpha = alpha;
   p.D = static_cast<uint16_t*>(D);
@@ -705,12 +748,14 @@ int launch_variant(const void* A, const void* B, const void* SFA, const void* SF
   p.M = M;
   p.N = N;
   p.K = K;
+  p.splits = splits;
+  p.partial = partial;
   p.tiles_m = (M + kBlockM * CG - 1) / (kBlockM * CG);
   p.tiles_n = N / BN;
   p.group_n = 8;
   const int sms = device_sm_count();
   if (sms <= 0) return B2_ERR_CUDA;
-  const int units = std::min(p.tiles_m * p.tiles_n, sms / CG);
+  const int units = std::min(p.tiles_m * p.tiles_n * splits, sms / CG);
 
   static bool configured = false;  // per template instantiation
   if (!configured) {
@@ -732,7 +777,80 @@ int launch_variant(const void* A, const void* B, const void* SFA, const void* SF
     cfg.numAttrs = 1;
   }
   B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps.a, maps.b, maps.sfa, maps.sfb, p));
+  if (splits > 1) {
+    const int64_t mn = static_cast<int64_t>(M) * N;
+    const int threads = 256;
+    const int64_t blocks = (mn / 8 + threads - 1) / threads;
+    splitk_reduce_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(partial, alpha, p.D, mn, splits);
+    B2_CUDA_TRY(cudaGetLastError());
+  }
   return B2_OK;
+}
+
+struct Scratch {
+  float* ptr = nullptr;
+  size_t bytes = 0;
+};
+Scratch g_scratch[64];
+
+// Per-device scratch for split-K partial sums, grown on demand (cudaFree synchronises the device,
+// so a buffer still in use by earlier launches is never released under them).
+int partial_scratch(size_t bytes, float** out) {
+  int dev = 0;
+  B2_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_mu);
+  Scratch& sc = g_scratch[dev & 63];
+  if (sc.bytes < bytes) {
+    if (sc.ptr) B2_CUDA_TRY(cudaFree(sc.ptr));
+    sc.ptr = nullptr;
+    sc.bytes = 0;
+    void* fresh = nullptr;
+    B2_CUDA_TRY(cudaMalloc(&fresh, bytes));
+    sc.ptr = static_cast<float*>(fresh);
+    sc.bytes = bytes;
+  }
+  *out = sc.ptr;
+  return B2_OK;
+}
+
+// K ranges for shapes with too few output tiles to occupy the GPU (decode-sized M): the largest
+// power of two that keeps every SM at most one work item, divides the slab count and leaves at
+// least four slabs per range.
+int choose_splits(int tiles, int k_slabs, int units_available) {
+  int splits = 1;
+  while (splits < 8 && tiles * splits * 2 <= units_available && k_slabs % (splits * 2) == 0 &&
+         k_slabs / (splits * 2) >= 4)
+    splits *= 2;
+  return splits;
+}
+
+template <int CG, int BN, int STAGES>
+int launch_variant(const void* A, const void* B, const void* SFA, const void* SFB, const float* alpha,
+                   void* D, int M, int N, int K, int variant, cudaStream_t stream) {
+  uint32_t* status = nullptr;
+  if (int rc = status_word(&status)) return rc;
+  MapSet maps;
+  {
+    const MapKey key{A, B, SFA, SFB, M, N, K, variant};
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_maps.find(key);
+    if (it == g_maps.end()) {
+      MapSet fresh;
+      if (int rc = encode_maps<CG, BN, STAGES>(&fresh, A, B, SFA, SFB, M, N, K)) return rc;
+      if (g_maps.size() > 4096) g_maps.clear();
+      it = g_maps.emplace(key, fresh).first;
+    }
+    maps = it->second;
+  }
+  const int sms = device_sm_count();
+  if (sms <= 0) return B2_ERR_CUDA;
+  const int tiles = ((M + kBlockM * CG - 1) / (kBlockM * CG)) * (N / BN);
+  const int splits = choose_splits(tiles, K / kBlockK, sms / CG);
+  float* partial = nullptr;
+  if (splits > 1) {
+    if (int rc = partial_scratch(static_cast<size_t>(splits) * M * N * sizeof(float), &partial)) return rc;
+  }
+  return launch_kernels<CG, BN, STAGES>(maps, alpha, D, M, N, K, splits, status, partial, stream);
 }
 
 int g_forced_variant = -1;  // test hook: -1 = automatic
@@ -778,8 +896,8 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
   int variant = g_forced_variant;
   if (variant < 0) {
     const bool pair_ok = M > 128;
-    if (N % 256 == 0) variant = pair_ok ? 2 : 1;
-    else variant = pair_ok ? 3 : 0;
+    if (!pair_ok) variant = 0;  // decode-sized M: more, narrower tiles (and K ranges) to fill the GPU
+    else variant = N % 256 == 0 ? 2 : 3;
   }
   if ((variant == 1 || variant == 2) && N % 256 != 0) {
     set_error("b2_nvfp4_gemm: variant %d needs N %% 256 == 0", variant);
