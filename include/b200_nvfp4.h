@@ -119,6 +119,27 @@ int b2_nvfp4_gemm_set_variant(int variant);
 int b2_nvfp4_gemm_status(void* stream);
 
 /*
+ * Decode-sized GEMM (1 <= M <= 128) for callers that must not allocate device memory.  It has no
+ * counterpart in the reference.  Same operands and result as b2_nvfp4_gemm, but neither this call
+ * nor its first-use set-up calls cudaMalloc, cudaFree or any allocating library routine: the
+ * partial sums of its split-K path and its status words live in a 4 MiB + 256 B array built
+ * into the library (resident on every GPU that loads it until the process exits).
+ * Meant for hosts where a plugin may not allocate: a serving loop that owns all of HBM through its
+ * own pool, a latency-critical section that cannot afford the device-wide synchronisation of
+ * cudaMalloc / cudaFree, a sandbox that forbids the call.
+ *  - The first call on a device resolves the array's device address; make it before any stream
+ *    capture.
+ *  - Problems whose partial sums (K ranges x M x N x 4 bytes) exceed 4 MiB are rejected with
+ *    B2_ERR_INVALID_ARGUMENT; b2_last_error() states the requirement and the limit.
+ *  - All calls on a device share the array: keep them in stream order, calls that overlap on the
+ *    GPU race on it.  Nothing has to be cleared between calls.
+ *  - Expired bounded waits end the kernel cleanly but are not reported through
+ *    b2_nvfp4_gemm_status.
+ */
+int b2_nvfp4_gemm_small_m_noalloc(const void* A, const void* B, const void* SFA, const void* SFB,
+                                  const float* alpha_dev, void* D, int M, int N, int K, void* stream);
+
+/*
  * In-kernel role timers of b2_nvfp4_gemm (observability; the reference's nearest analogue is the
  * u64 event buffer of tirx_kernels/basic/allgather_gemm.py:48-53).  `enable` != 0 makes later
  * launches record, for CTA 0, SM-cycle counters per warp role; `out12` (host, may be NULL)

@@ -949,3 +949,104 @@ extern "C" int b2_nvfp4_gemm_status(void* stream) {
             host[1]);
   return B2_ERR_DEVICE_TIMEOUT;
 }
+
+// ---- decode-sized GEMM for callers that must not allocate ---------------------------------------
+//
+// Some hosts of this library run where device allocation is off the table: a serving loop that
+// has handed every byte of HBM to its own pool and treats a cudaMalloc from a plugin as a bug, a
+// caller inside a latency-critical section where the implicit device synchronisation of
+// cudaMalloc / cudaFree would stall every stream, or a sandboxed plugin host that simply forbids
+// the call.  b2_nvfp4_gemm allocates on such a caller's behalf (its status word on first use,
+// and a scratch buffer for the partial sums of its split-K path).  The entry point below does
+// the same decode-sized product with all of that scratch placed in one array that is part of the
+// library image itself.
+namespace b2 {
+namespace {
+
+constexpr size_t kBuiltinPartialBytes = 4u << 20;  // room for the fp32 partial sums: 4 MiB
+constexpr size_t kBuiltinStatusBytes = 256;        // status words and role timers
+// Lives in every GPU context that loads the library, until the process exits.
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinPartialBytes + kBuiltinStatusBytes];
+
+// Device address of the array per device ordinal.  In host code `g_builtin_scratch` names a
+// host-side shadow of the symbol, not device memory, so the address a kernel may use has to be
+// asked for, once per device and with that device current.
+unsigned char* g_builtin_base[64] = {nullptr};
+
+int builtin_scratch(unsigned char** out) {
+  int dev = 0;
+  B2_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    set_error("device ordinal %d out of range", dev);
+    return B2_ERR_CUDA;
+  }
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (!g_builtin_base[dev]) {
+    void* ptr = nullptr;
+    B2_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_builtin_scratch));
+    g_builtin_base[dev] = static_cast<unsigned char*>(ptr);
+  }
+  *out = g_builtin_base[dev];
+  return B2_OK;
+}
+
+}  // namespace
+}  // namespace b2
+
+// D[M,N] (bf16) = alpha * A[M,K] * B[N,K]^T for M <= 128, same operands and result as
+// b2_nvfp4_gemm, without any device allocation: no cudaMalloc, cudaFree or allocating library
+// routine is called, here or on first use.  The split-K partial sums and the kernel's status
+// words live in an array built into the library (4 MiB + 256 B per GPU that loads it).
+//
+//  * The first call on a device looks the array's device address up (cudaGetSymbolAddress) and
+//    sets the kernel's shared-memory attribute; make that first call before any stream capture.
+//  * A problem whose partial sums (K ranges x M x N x 4 bytes, the ranges chosen as in
+//    b2_nvfp4_gemm) exceed 4 MiB is rejected with B2_ERR_INVALID_ARGUMENT and nothing is launched.
+//  * Every call on a device uses the same array, which keeps the previous call's contents.  Each
+//    call overwrites all partial sums it later reads, so nothing needs clearing, but two calls
+//    that overlap on the GPU (different streams, or graphs replayed concurrently) race on it:
+//    keep calls of this entry point on one device in stream order.
+//  * Tensor maps are encoded on every call instead of being cached.  A bounded wait that expires
+//    still ends the kernel cleanly, but its code is written to the built-in status words, which
+//    b2_nvfp4_gemm_status does not read.
+extern "C" int b2_nvfp4_gemm_small_m_noalloc(const void* A, const void* B, const void* SFA, const void* SFB,
+                                             const float* alpha_dev, void* D, int M, int N, int K,
+                                             void* stream) {
+  using namespace b2;
+  if (!A || !B || !SFA || !SFB || !alpha_dev || !D) {
+    set_error("b2_nvfp4_gemm_small_m_noalloc: null pointer argument");
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (M < 1 || M > kBlockM || N < 1 || K < 1 || K % 256 != 0 || N % 128 != 0) {
+    set_error("b2_nvfp4_gemm_small_m_noalloc: M=%d N=%d K=%d: need 1 <= M <= 128, N %% 128 == 0, K %% 256 == 0",
+              M, N, K);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  const uintptr_t all = reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
+                        reinterpret_cast<uintptr_t>(SFA) | reinterpret_cast<uintptr_t>(SFB) |
+                        reinterpret_cast<uintptr_t>(D);
+  if (all & 15) {
+    set_error("b2_nvfp4_gemm_small_m_noalloc: all tensors must be 16-byte aligned");
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (!encode_tiled_fn()) {
+    set_error("b2_nvfp4_gemm_small_m_noalloc: cuTensorMapEncodeTiled is not available from this driver");
+    return B2_ERR_CUDA;
+  }
+  const int sms = device_sm_count();
+  if (sms <= 0) return B2_ERR_CUDA;
+  const int splits = choose_splits(N / 128, K / kBlockK, sms);
+  const size_t need = splits > 1 ? static_cast<size_t>(splits) * M * N * sizeof(float) : 0;
+  if (need > kBuiltinPartialBytes) {
+    set_error("b2_nvfp4_gemm_small_m_noalloc: M=%d N=%d needs %zu bytes of partial sums, the built-in scratch "
+              "holds %zu; use b2_nvfp4_gemm", M, N, need, kBuiltinPartialBytes);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  unsigned char* base = nullptr;
+  if (int rc = builtin_scratch(&base)) return rc;
+  MapSet maps;
+  if (int rc = encode_maps<1, 128, 6>(&maps, A, B, SFA, SFB, M, N, K)) return rc;
+  return launch_kernels<1, 128, 6>(maps, alpha_dev, D, M, N, K, splits,
+                                   reinterpret_cast<uint32_t*>(base + kBuiltinPartialBytes),
+                                   reinterpret_cast<float*>(base), static_cast<cudaStream_t>(stream));
+}

@@ -31,6 +31,7 @@ MAIN_SIGNATURES = {
     "b2_nvfp4_sf_bytes": (_i64, [_i, _i, _i]),
     "b2_rmsnorm_fp4quant": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _vp]),
     "b2_nvfp4_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "b2_nvfp4_gemm_small_m_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "b2_nvfp4_gemm_status": (_i, [_vp]),
     "b2_nvfp4_gemm_set_variant": (_i, [_i]),
     "b2_nvfp4_gemm_role_timers": (_i, [_i, _vp, _vp]),
@@ -163,6 +164,16 @@ def nvfp4_gemm(A, B, SFA, SFB, alpha, D, M: int, N: int, K: int) -> None:
         lib().b2_nvfp4_gemm(_ptr(A), _ptr(B), _ptr(SFA), _ptr(SFB), _ptr(alpha), _ptr(D), M, N, K,
                             current_stream_ptr()),
         "b2_nvfp4_gemm",
+    )
+
+
+def nvfp4_gemm_small_m_noalloc(A, B, SFA, SFB, alpha, D, M: int, N: int, K: int) -> None:
+    """Decode-sized GEMM whose scratch is built into the library: for callers that may not allocate."""
+    _require_cuda(A, B, SFA, SFB, alpha, D)
+    check(
+        lib().b2_nvfp4_gemm_small_m_noalloc(_ptr(A), _ptr(B), _ptr(SFA), _ptr(SFB), _ptr(alpha), _ptr(D),
+                                            M, N, K, current_stream_ptr()),
+        "b2_nvfp4_gemm_small_m_noalloc",
     )
 
 
