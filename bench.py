@@ -384,6 +384,44 @@ def ffn_sharded(rank: int, world: int, distributed: bool, M: int = 8192, N: int 
     t_ag = phase_us(gather) if distributed else 0.0
     t_all = phase_us(whole)
     _native.nvfp4_gemm_status()
+
+    # fused path: the GEMM epilogue stores every tile into all GPUs' [M, N] buffers over NVLink; two buffer
+    # sets alternate so that one barrier per step is enough
+    fused = {}
+    if distributed:
+        sets = [ffn_tp.PeerOutputBuffers(M, N, world, rank) for _ in range(2)]
+        turn = [0]
+
+        def fused_gemm():
+            buf = sets[turn[0] & 1]
+            turn[0] += 1
+            _native.nvfp4_gemm_allgather(A_fp4, B_fp4, A_sf, B_sf, alpha_t, buf.addresses, rank, M, shard, K)
+            torch.distributed.all_reduce(token)
+
+        def fused_whole():
+            buf = sets[turn[0] & 1]
+            turn[0] += 1
+            ffn_tp.fused_forward(projection, act, buf)
+
+        token = torch.zeros(1, device="cuda")
+        whole()
+        turn[0] = 0
+        fused_whole()
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        identical = bool(torch.equal(sets[0].local, ffn_tp.assemble(gathered)))
+        t_fg, t_fall = phase_us(fused_gemm), phase_us(fused_whole)
+        _native.nvfp4_gemm_status()
+        fused = {
+            "fused_gemm_allgather_us": t_fg, "fused_step_us": t_fall,
+            "fused_equals_nccl_path": identical,
+            "fused_total_tflops": gemm.flops(M, N, K) / t_fall / 1e6,
+            "fused_send_gbs": (world - 1) * M * shard * 2 / t_fg / 1e3,
+        }
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        for buf in sets:
+            buf.close()
     result = {
         "M": M, "N": N, "K": K, "world": world, "shard_n": shard,
         "quantize_us": t_q, "gemm_us": t_g, "allgather_us": t_ag, "step_us": t_all,
@@ -392,6 +430,7 @@ def ffn_sharded(rank: int, world: int, distributed: bool, M: int = 8192, N: int 
         "quantize_roofline": _checks.roofline_hbm(M * K * 2 + M * K // 2 + M * K // 16 + 4, t_q),
         "total_tflops": gemm.flops(M, N, K) / t_all / 1e6, "scaling": "strong",
     }
+    result.update(fused)
     if distributed:
         received = (world - 1) * M * shard * 2
         result["allgather_recv_gbs"] = received / t_ag / 1e3

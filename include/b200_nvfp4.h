@@ -140,6 +140,34 @@ int b2_nvfp4_gemm_small_m_noalloc(const void* A, const void* B, const void* SFA,
                                   const float* alpha_dev, void* D, int M, int N, int K, void* stream);
 
 /*
+ * Column-sharded projection with its output all-gather fused into the GEMM epilogue, for the
+ * tensor-parallel FFN.  The reference's nearest analogues are tirx_kernels/basic/allgather_gemm.py
+ * (peer puts of the INPUT rows in front of an fp16 GEMM) and tirx_kernels/basic/gemm_reduce_scatter.py
+ * (GEMM with a fused collective on its output); it has no NVFP4 form of either.
+ *
+ * One process per GPU.  Every GPU owns one bf16 buffer [M, world * N] obtained from b2_peer_alloc;
+ * b2_peer_export turns it into a 64-byte handle that the ranks exchange over their own control
+ * channel, and b2_peer_open maps a peer's handle into this process (b2_peer_close unmaps it,
+ * b2_peer_free releases the owner's buffer).  `D_all[g]` is this process's address of GPU g's buffer
+ * (its own allocation for g == rank).
+ *
+ * b2_nvfp4_gemm_allgather multiplies A [M, K] by this rank's weight slab B [N, K] and stores every
+ * finished tile into columns [rank * N, (rank + 1) * N) of all `world` buffers: the local one with
+ * ordinary stores, the others with stores over NVLink.  No remote load, no multicast.  The call
+ * is asynchronous; a peer's rows are complete only after that peer's stream has passed the call, so
+ * the caller runs a cross-rank barrier (any host or NCCL barrier ordered after the stream) before
+ * reading.  Needs M > 128, N % 128 == 0, K % 256 == 0, 1 <= world <= 8.
+ */
+int b2_peer_alloc(void** ptr, int64_t bytes);
+int b2_peer_free(void* ptr);
+int b2_peer_export(void* ptr, unsigned char* handle64);
+int b2_peer_open(const unsigned char* handle64, void** ptr);
+int b2_peer_close(void* ptr);
+int b2_nvfp4_gemm_allgather(const void* A, const void* B, const void* SFA, const void* SFB,
+                            const float* alpha_dev, void* const* D_all, int world, int rank,
+                            int M, int N, int K, void* stream);
+
+/*
  * In-kernel role timers of b2_nvfp4_gemm (observability; the reference's nearest analogue is the
  * u64 event buffer of tirx_kernels/basic/allgather_gemm.py:48-53).  `enable` != 0 makes later
  * launches record, for CTA 0, SM-cycle counters per warp role; `out12` (host, may be NULL)

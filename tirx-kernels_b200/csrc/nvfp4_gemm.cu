@@ -24,6 +24,7 @@
 // (tensor memory released); the host reads the word through b2_nvfp4_gemm_status().
 #include <cuda.h>
 
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -39,7 +40,10 @@ constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;  // one second p
 
 struct GemmParams {
   const float* alpha;
-  uint16_t* D;
+  uint16_t* D;       // output (direct-store epilogue)
+  int n_dest;        // TMA-store epilogue: buffers every tile is stored to (this GPU's own first)
+  int ldd;           // elements between output rows (N, or world * N for the gathered layout)
+  int col0;          // first output column of this GPU's slab inside the gathered row
   uint32_t* status;  // [0]: first failure code, [1]: detail; role timers from byte 64 on
   int profile;       // CTA 0 records per-role cycle counters when set
   int M, N, K;
@@ -232,7 +236,7 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
 }
 
 // ---- shared memory ------------------------------------------------------------------------------
-template <int CG, int BN, int STAGES>
+template <int CG, int BN, int STAGES, bool TMA_OUT = false>
 struct SmemLayout {
   static constexpr int kBRows = BN / CG;                       // rows of B held by one CTA
   static constexpr int kChunks = BN / 128 > 0 ? BN / 128 : 1;  // 128-row scale chunks of B
@@ -243,7 +247,13 @@ struct SmemLayout {
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr int kSfCols = 16 + 16 * kChunks;            // TMEM columns of one stage's scales
   static constexpr int kBarrierBytes = 512;
-  static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  // output staging of the TMA-store epilogue: per epilogue warp 32 rows x BN/2 columns of bf16,
+  // cut into 32 x 64 sub-tiles of 4 KB (128-byte rows, 128-byte swizzle)
+  static constexpr int kStagingBytes = TMA_OUT ? kBlockM * BN * 2 : 0;
+  static constexpr int kRingBytes = STAGES * kStageBytes + kStagingBytes;
+  static constexpr int kTotal = kRingBytes + kBarrierBytes + 1024;  // + alignment slack
+  static_assert(kStageBytes % 1024 == 0, "stages and staging stay 1024-byte aligned");
+  static_assert(kTotal <= 227 * 1024, "shared memory budget");
   static_assert(BN + STAGES * kSfCols <= 512, "tensor memory budget");
   static_assert((4 * STAGES + 2) * 8 + 16 <= kBarrierBytes, "barrier area");
 };
@@ -303,12 +313,33 @@ __device__ __forceinline__ void tmem_st_wait() {
 // tensor memory the warp is allowed to touch.
 constexpr int kWarpProducer = 0, kWarpMma = 1, kWarpScale0 = 2, kWarpEpi0 = 10;
 
-template <int CG, int BN, int STAGES>
+// Output tensor maps of the TMA-store epilogue: [0] this GPU's buffer, [1..] the peers' buffers.
+template <bool TMA_OUT>
+struct OutMaps {};
+template <>
+struct OutMaps<true> {
+  CUtensorMap m[8];
+};
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x),
+               "r"(y), "r"(smem)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+template <int CG, int BN, int STAGES, bool TMA_OUT>
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                      const __grid_constant__ GemmParams p) {
-  using L = SmemLayout<CG, BN, STAGES>;
+                      const __grid_constant__ GemmParams p, const __grid_constant__ OutMaps<TMA_OUT> out_maps) {
+  using L = SmemLayout<CG, BN, STAGES, TMA_OUT>;
   constexpr int kTmemCols = 512;
   constexpr uint32_t kIdesc = instr_desc(kBlockM * CG, BN);
   constexpr uint32_t kOperandTx = static_cast<uint32_t>(L::kABytes + L::kBBytes) * CG;
@@ -317,7 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t bar_base = smem_base + STAGES * L::kStageBytes;
+  const uint32_t bar_base = smem_base + L::kRingBytes;
   // full: A and B of a stage landed (CTA pair: counted on the leader for both CTAs);
   // sfload: this CTA's scale blocks landed; sfready: scales are in tensor memory (on the leader,
   // one arrive per scale warp of the group); empty: the stage's MMAs retired.
@@ -327,7 +358,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   auto empty_bar = [&](int s) { return bar_base + 8u * (3 * STAGES + s); };
   const uint32_t tmem_full_bar = bar_base + 8u * (4 * STAGES);
   const uint32_t tmem_empty_bar = bar_base + 8u * (4 * STAGES + 1);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * L::kStageBytes + 8 * (4 * STAGES + 2));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + L::kRingBytes + 8 * (4 * STAGES + 2));
   volatile uint32_t* abort_flag = tmem_slot + 1;
   const WaitCtx ctx{p.status, abort_flag};
 
@@ -519,7 +550,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       t_wait += w1 - w0;
       tc_fence_after();
       const int row = (tm * CG + static_cast<int>(rank)) * kBlockM + quarter * 32 + lane;
-      uint16_t* drow = p.D + static_cast<int64_t>(row) * p.N + static_cast<int64_t>(tn) * BN + half * kHalf;
+      const int64_t doff = static_cast<int64_t>(row) * p.ldd + p.col0 + static_cast<int64_t>(tn) * BN + half * kHalf;
+      uint16_t* drow = p.D + doff;
       // Drain this warp's part of the accumulator into registers as packed bf16, hand tensor memory
       // back to the MMA warp, and only then write to global memory: the next tile's MMAs overlap
       // the stores.
@@ -548,6 +580,49 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (eprof) { t_body += clock64() - w1; ++n_tiles; }
         continue;
       }
+      if constexpr (TMA_OUT) {
+        // Drain through shared memory: each lane owns one row and writes 16-byte chunks at their
+        // 128-byte-swizzled position (conflict-free), then one lane hands every 32 x 64 sub-tile to
+        // the TMA, once per destination buffer.  Rows past M are clipped by the tensor map.  The
+        // stores run while the next tile is multiplied; peers are reached by stores only.
+        const uint32_t staging = smem_base + STAGES * L::kStageBytes +
+                                 static_cast<uint32_t>(warp - kWarpEpi0) * (kHalf / 64) * 4096u;
+        if (lane == 0) bulk_wait_read_all();  // the previous tile's stores have read the staging
+        __syncwarp();
+#pragma unroll
+        for (int c0 = 0; c0 < kHalf; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * kHalf + c0, v);
+          tmem_ld_wait();
+          const uint32_t sub = staging + (c0 / 64) * 4096u + lane * 128u;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              w[i] = pack_from_f32<BF16Tag>(__uint_as_float(v[8 * j + 2 * i]) * alpha,
+                                            __uint_as_float(v[8 * j + 2 * i + 1]) * alpha);
+            const uint32_t chunk = static_cast<uint32_t>((c0 % 64) / 8 + j) ^ (lane & 7u);
+            sts128(sub + chunk * 16u, w[0], w[1], w[2], w[3]);
+          }
+        }
+        tc_fence_before();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive_local(tmem_empty_bar);
+          else mbar_arrive_cluster_relaxed(empty_target);
+          const int row0 = (tm * CG + static_cast<int>(rank)) * kBlockM + quarter * 32;
+          if (row0 < p.M) {
+            const int x0 = p.col0 + tn * BN + half * kHalf;
+            for (int d = 0; d < p.n_dest; ++d)
+#pragma unroll
+              for (int sub = 0; sub < kHalf / 64; ++sub)
+                tma_store_2d(&out_maps.m[d], staging + sub * 4096u, x0 + sub * 64, row0);
+          }
+          bulk_commit();
+        }
+      } else {
       uint32_t packed[kHalf / 2];
 #pragma unroll
       for (int c0 = 0; c0 < kHalf; c0 += 32) {
@@ -571,8 +646,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int i = 0; i < kHalf / 8; ++i)
           dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
       }
+      }
       acc_phase ^= 1u;
       if (eprof) { t_body += clock64() - w1; ++n_tiles; }
+    }
+    if constexpr (TMA_OUT) {
+      if (lane == 0) bulk_wait_all();  // every store has left shared memory and is written
     }
     if (eprof) {
       counters[6] = t_wait;
@@ -735,14 +814,40 @@ int encode_maps(MapSet* maps, const void* A, const void* B, const void* SFA, con
 }
 
 // Launches the GEMM (and, with splits > 1, the reduction) on prepared tensor maps and scratch.
-template <int CG, int BN, int STAGES>
+struct GatherTarget {  // the gathered output layout: row length and this GPU's first column in it
+  int n_dest = 0;
+  int ldd = 0;   // 0: N
+  int col0 = 0;
+};
+
+// One 32-row x 64-column store box of a bf16 [M, ldd] output, 128-byte swizzled in shared memory.
+int encode_output_map(CUtensorMap* map, void* base, int M, int ldd) {
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(ldd), static_cast<cuuint64_t>(M)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldd) * 2};
+  const cuuint32_t box[2] = {64, 32};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, elem,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled(output) failed with %d", static_cast<int>(r));
+    return B2_ERR_CUDA;
+  }
+  return B2_OK;
+}
+
+template <int CG, int BN, int STAGES, bool TMA_OUT = false>
 int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N, int K, int splits,
-                   uint32_t* status, float* partial, cudaStream_t stream) {
-  using L = SmemLayout<CG, BN, STAGES>;
-  auto kernel = nvfp4_gemm_kernel<CG, BN, STAGES>;
+                   uint32_t* status, float* partial, cudaStream_t stream, const GatherTarget& gather = GatherTarget(),
+                   const OutMaps<TMA_OUT>& out_maps = OutMaps<TMA_OUT>()) {
+  using L = SmemLayout<CG, BN, STAGES, TMA_OUT>;
+  auto kernel = nvfp4_gemm_kernel<CG, BN, STAGES, TMA_OUT>;
   GemmParams p;
   p.alpha = alpha;
   p.D = static_cast<uint16_t*>(D);
+  p.n_dest = gather.n_dest;
+  p.ldd = gather.ldd ? gather.ldd : N;
+  p.col0 = gather.col0;
   p.status = status;
   p.profile = g_profile;
   p.M = M;
@@ -776,7 +881,7 @@ int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N
     cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
-  B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps.a, maps.b, maps.sfa, maps.sfb, p));
+  B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps.a, maps.b, maps.sfa, maps.sfb, p, out_maps));
   if (splits > 1) {
     const int64_t mn = static_cast<int64_t>(M) * N;
     const int threads = 256;
@@ -1049,4 +1154,108 @@ extern "C" int b2_nvfp4_gemm_small_m_noalloc(const void* A, const void* B, const
   return launch_kernels<1, 128, 6>(maps, alpha_dev, D, M, N, K, splits,
                                    reinterpret_cast<uint32_t*>(base + kBuiltinPartialBytes),
                                    reinterpret_cast<float*>(base), static_cast<cudaStream_t>(stream));
+}
+
+// ---- sharded projection: GEMM with the output all-gather fused into its epilogue ---------------
+//
+// Every GPU owns one [M, world * N] bf16 buffer allocated with b2_peer_alloc and mapped into
+// the other processes through CUDA IPC.  GPU `rank` multiplies by its N-row slab of the weight and
+// its epilogue stores each finished tile into column range [rank * N, (rank + 1) * N) of ALL
+// `world` buffers (its own through `D_all[rank]`, the others over NVLink).  Only stores cross the
+// link; there is no remote load and no multicast.  The caller orders a cross-rank barrier after the
+// launch before anyone reads the gathered rows.
+extern "C" int b2_peer_alloc(void** ptr, int64_t bytes) {
+  using namespace b2;
+  if (!ptr || bytes <= 0) {
+    set_error("b2_peer_alloc: bad arguments");
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  B2_CUDA_TRY(cudaMalloc(ptr, static_cast<size_t>(bytes)));
+  return B2_OK;
+}
+
+extern "C" int b2_peer_free(void* ptr) {
+  using namespace b2;
+  B2_CUDA_TRY(cudaFree(ptr));
+  return B2_OK;
+}
+
+extern "C" int b2_peer_export(void* ptr, unsigned char* handle64) {
+  using namespace b2;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  if (!ptr || !handle64) {
+    set_error("b2_peer_export: null argument");
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  cudaIpcMemHandle_t handle;
+  B2_CUDA_TRY(cudaIpcGetMemHandle(&handle, ptr));
+  memcpy(handle64, &handle, 64);
+  return B2_OK;
+}
+
+extern "C" int b2_peer_open(const unsigned char* handle64, void** ptr) {
+  using namespace b2;
+  if (!ptr || !handle64) {
+    set_error("b2_peer_open: null argument");
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  cudaIpcMemHandle_t handle;
+  memcpy(&handle, handle64, 64);
+  B2_CUDA_TRY(cudaIpcOpenMemHandle(ptr, handle, cudaIpcMemLazyEnablePeerAccess));
+  return B2_OK;
+}
+
+extern "C" int b2_peer_close(void* ptr) {
+  using namespace b2;
+  B2_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return B2_OK;
+}
+
+extern "C" int b2_nvfp4_gemm_allgather(const void* A, const void* B, const void* SFA, const void* SFB,
+                                       const float* alpha_dev, void* const* D_all, int world, int rank,
+                                       int M, int N, int K, void* stream) {
+  using namespace b2;
+  if (!A || !B || !SFA || !SFB || !alpha_dev || !D_all) {
+    set_error("b2_nvfp4_gemm_allgather: null pointer argument");
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) {
+    set_error("b2_nvfp4_gemm_allgather: rank %d of world %d (1..8 GPUs of one box)", rank, world);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (M <= 128 || N < 1 || K < 1 || K % 256 != 0 || N % 128 != 0) {
+    set_error("b2_nvfp4_gemm_allgather: M=%d N=%d K=%d: need M > 128, N %% 128 == 0, K %% 256 == 0", M, N, K);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  for (int g = 0; g < world; ++g) {
+    if (!D_all[g] || (reinterpret_cast<uintptr_t>(D_all[g]) & 31)) {
+      set_error("b2_nvfp4_gemm_allgather: output buffer %d is null or not 32-byte aligned", g);
+      return B2_ERR_INVALID_ARGUMENT;
+    }
+  }
+  if (!encode_tiled_fn()) {
+    set_error("b2_nvfp4_gemm_allgather: cuTensorMapEncodeTiled is not available from this driver");
+    return B2_ERR_CUDA;
+  }
+  uint32_t* status = nullptr;
+  if (int rc = status_word(&status)) return rc;
+  // destination 0 is this GPU's buffer, then the peers in ring order starting after this rank, so
+  // that the GPUs do not all write to the same one at the same time
+  OutMaps<true> out_maps;
+  for (int i = 0; i < world; ++i)
+    if (int rc = encode_output_map(&out_maps.m[i], D_all[(rank + i) % world], M, world * N)) return rc;
+  GatherTarget gather;
+  gather.n_dest = world;
+  gather.ldd = world * N;
+  gather.col0 = rank * N;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  MapSet maps;
+  if (N % 256 == 0) {
+    if (int rc = encode_maps<2, 256, 4>(&maps, A, B, SFA, SFB, M, N, K)) return rc;
+    return launch_kernels<2, 256, 4, true>(maps, alpha_dev, D_all[rank], M, N, K, 1, status, nullptr, s, gather,
+                                           out_maps);
+  }
+  if (int rc = encode_maps<2, 128, 6>(&maps, A, B, SFA, SFB, M, N, K)) return rc;
+  return launch_kernels<2, 128, 6, true>(maps, alpha_dev, D_all[rank], M, N, K, 1, status, nullptr, s, gather,
+                                         out_maps);
 }

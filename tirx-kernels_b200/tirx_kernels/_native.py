@@ -36,6 +36,12 @@ MAIN_SIGNATURES = {
     "b2_nvfp4_gemm_set_variant": (_i, [_i]),
     "b2_nvfp4_gemm_role_timers": (_i, [_i, _vp, _vp]),
     "b2_mufu_probe": (_i, [_i, _vp, _vp, _i, _vp]),
+    "b2_peer_alloc": (_i, [ctypes.POINTER(ctypes.c_void_p), _i64]),
+    "b2_peer_free": (_i, [_vp]),
+    "b2_peer_export": (_i, [_vp, ctypes.c_char_p]),
+    "b2_peer_open": (_i, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
+    "b2_peer_close": (_i, [_vp]),
+    "b2_nvfp4_gemm_allgather": (_i, [_vp, _vp, _vp, _vp, _vp, ctypes.POINTER(ctypes.c_void_p), _i, _i, _i, _i, _i, _vp]),
 }
 CUBLASLT_SIGNATURES = {
     "b2_nvfp4_gemm_cublaslt": (_i, [_vp, _vp, _vp, _vp, _f, _vp, _i, _i, _i, _vp]),
@@ -174,6 +180,50 @@ def nvfp4_gemm_small_m_noalloc(A, B, SFA, SFB, alpha, D, M: int, N: int, K: int)
         lib().b2_nvfp4_gemm_small_m_noalloc(_ptr(A), _ptr(B), _ptr(SFA), _ptr(SFB), _ptr(alpha), _ptr(D),
                                             M, N, K, current_stream_ptr()),
         "b2_nvfp4_gemm_small_m_noalloc",
+    )
+
+
+def peer_alloc(nbytes: int) -> int:
+    """Device allocation that can be exported to the other processes of the box; returns its address."""
+    ptr = ctypes.c_void_p()
+    check(lib().b2_peer_alloc(ctypes.byref(ptr), int(nbytes)), "b2_peer_alloc")
+    return int(ptr.value)
+
+
+def peer_free(ptr: int) -> None:
+    check(lib().b2_peer_free(ptr), "b2_peer_free")
+
+
+def peer_export(ptr: int) -> bytes:
+    handle = ctypes.create_string_buffer(64)
+    check(lib().b2_peer_export(ptr, handle), "b2_peer_export")
+    return handle.raw
+
+
+def peer_open(handle: bytes) -> int:
+    if len(handle) != 64:
+        raise ValueError("a peer handle is 64 bytes")
+    ptr = ctypes.c_void_p()
+    check(lib().b2_peer_open(handle, ctypes.byref(ptr)), "b2_peer_open")
+    return int(ptr.value)
+
+
+def peer_close(ptr: int) -> None:
+    check(lib().b2_peer_close(ptr), "b2_peer_close")
+
+
+def nvfp4_gemm_allgather(A, B, SFA, SFB, alpha, buffers, rank: int, M: int, N: int, K: int) -> None:
+    """GEMM by this rank's weight slab; tiles land in columns [rank*N, (rank+1)*N) of every buffer.
+
+    `buffers` are this process's addresses of all ranks' [M, world*N] bf16 buffers, in rank order.
+    """
+    _require_cuda(A, B, SFA, SFB, alpha)
+    world = len(buffers)
+    array = (ctypes.c_void_p * world)(*[int(b) for b in buffers])
+    check(
+        lib().b2_nvfp4_gemm_allgather(_ptr(A), _ptr(B), _ptr(SFA), _ptr(SFB), _ptr(alpha), array, world,
+                                      int(rank), M, N, K, current_stream_ptr()),
+        "b2_nvfp4_gemm_allgather",
     )
 
 

@@ -80,3 +80,89 @@ class ShardedProjection:
             gather = lambda dst, src: dist.all_gather_into_tensor(dst, src)
         gather(gathered.reshape(-1), out.reshape(-1))
         return gathered
+
+
+class _RawDeviceMemory:
+    """Exposes a raw device address to torch through the CUDA array interface (as int16 words)."""
+
+    def __init__(self, ptr: int, words: int):
+        self.__cuda_array_interface__ = {
+            "shape": (words,),
+            "typestr": "<i2",
+            "data": (int(ptr), False),
+            "version": 3,
+            "strides": None,
+        }
+
+
+class PeerOutputBuffers:
+    """One ``[M, world * shard]`` bf16 buffer per GPU, each mapped into every process of the box.
+
+    The fused path (``b2_nvfp4_gemm_allgather``) stores its tiles into all of them, so after a
+    cross-rank barrier every GPU holds the row-major ``[M, N]`` result with no separate gather and
+    no re-layout.  Handles travel through ``torch.distributed`` (any backend); the memory itself is
+    allocated and mapped by the C-ABI library.  ``local`` is a torch view of this rank's buffer.
+    """
+
+    def __init__(self, m: int, n: int, world: int, rank: int, group=None):
+        import torch
+        import torch.distributed as dist
+
+        from .. import _native
+
+        shard_rows(n, world, rank)
+        self.m, self.n, self.world, self.rank = m, n, world, rank
+        self.nbytes = m * n * 2
+        self._native = _native
+        self._own = _native.peer_alloc(self.nbytes)
+        self._opened: list[int] = []
+        self.addresses = [0] * world
+        self.addresses[rank] = self._own
+        if world > 1:
+            handle = _native.peer_export(self._own)
+            handles: list = [None] * world
+            dist.all_gather_object(handles, handle, group=group)
+            for g, h in enumerate(handles):
+                if g == rank:
+                    continue
+                ptr = _native.peer_open(h)
+                self._opened.append(ptr)
+                self.addresses[g] = ptr
+        self.local = torch.as_tensor(_RawDeviceMemory(self._own, m * n), device="cuda").view(torch.bfloat16).view(m, n)
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's; every rank calls it after a barrier."""
+        for ptr in self._opened:
+            self._native.peer_close(ptr)
+        self._opened = []
+        if self._own:
+            self.local = None
+            self._native.peer_free(self._own)
+            self._own = 0
+
+
+def fused_forward(proj: ShardedProjection, act, buffers: PeerOutputBuffers, barrier: Callable | None = None):
+    """Quantize, then GEMM with the all-gather done by the GEMM's own epilogue over peer stores.
+
+    Returns the row-major ``[M, N]`` tensor on this GPU.  `barrier()` must order every rank's GEMM
+    before any rank's read (default: a one-element NCCL all-reduce on the current stream).  A caller
+    that runs steps back to back alternates between two `PeerOutputBuffers`, so that a fast rank's
+    next step cannot overwrite rows a slow rank is still reading.
+    """
+    from .. import _native
+
+    A_fp4, A_sf = proj.quantize(act)
+    _native.nvfp4_gemm_allgather(A_fp4, proj.B_fp4, A_sf, proj.B_sf, proj.alpha, buffers.addresses,
+                                 proj.rank, proj.m, proj.shard, proj.k)
+    if proj.world > 1:
+        if barrier is None:
+            import torch
+            import torch.distributed as dist
+
+            token = getattr(buffers, "_token", None)
+            if token is None:
+                token = buffers._token = torch.zeros(1, device="cuda")
+            dist.all_reduce(token)
+        else:
+            barrier()
+    return buffers.local
