@@ -929,7 +929,7 @@ int choose_splits(int tiles, int k_slabs, int units_available) {
   return splits;
 }
 
-template <int CG, int BN, int STAGES>
+template <int CG, int BN, int STAGES, bool TMA_OUT = false>
 int launch_variant(const void* A, const void* B, const void* SFA, const void* SFB, const float* alpha,
                    void* D, int M, int N, int K, int variant, cudaStream_t stream) {
   uint32_t* status = nullptr;
@@ -955,7 +955,26 @@ int launch_variant(const void* A, const void* B, const void* SFA, const void* SF
   if (splits > 1) {
     if (int rc = partial_scratch(static_cast<size_t>(splits) * M * N * sizeof(float), &partial)) return rc;
   }
-  return launch_kernels<CG, BN, STAGES>(maps, alpha, D, M, N, K, splits, status, partial, stream);
+  if constexpr (TMA_OUT) {
+    OutMaps<true> out_maps;
+    {
+      const MapKey key{D, nullptr, nullptr, nullptr, M, N, 0, -1};
+      std::lock_guard<std::mutex> lock(g_mu);
+      auto it = g_maps.find(key);
+      if (it == g_maps.end()) {
+        MapSet fresh;
+        if (int rc = encode_output_map(&fresh.a, D, M, N)) return rc;
+        it = g_maps.emplace(key, fresh).first;
+      }
+      out_maps.m[0] = it->second.a;
+    }
+    GatherTarget target;
+    target.n_dest = 1;
+    return launch_kernels<CG, BN, STAGES, true>(maps, alpha, D, M, N, K, splits, status, partial, stream, target,
+                                                out_maps);
+  } else {
+    return launch_kernels<CG, BN, STAGES>(maps, alpha, D, M, N, K, splits, status, partial, stream);
+  }
 }
 
 int g_forced_variant = -1;  // test hook: -1 = automatic
@@ -1011,8 +1030,8 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
   switch (variant) {
     case 0: return launch_variant<1, 128, 6>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 0, s);
     case 1: return launch_variant<1, 256, 4>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 1, s);
-    case 2: return launch_variant<2, 256, 5>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 2, s);
-    default: return launch_variant<2, 128, 8>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
+    case 2: return launch_variant<2, 256, 4, true>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 2, s);
+    default: return launch_variant<2, 128, 6, true>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
   }
 }
 
