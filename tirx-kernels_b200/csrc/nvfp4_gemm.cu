@@ -5,19 +5,25 @@
 // alpha then bf16 in the epilogue :795-800).  The kernel itself is written from scratch:
 //
 //   * persistent CTAs (or CTA pairs), one per SM, walking a grouped tile order;
-//   * warp 0: TMA producer  - A, B and both scale-factor blocks of a 256-wide K slab
-//             land in a ring of shared-memory stages, completion counted on an mbarrier;
-//   * warp 1: MMA issuer    - copies the slab's scale factors into tensor memory with
-//             tcgen05.cp, then issues four tcgen05.mma.kind::mxf4nvf4.block_scale
-//             (K = 64 each) accumulating into TMEM; tcgen05.commit releases the stage;
-//   * warps 2-5: epilogue   - tcgen05.ld the accumulator, scale by alpha, convert to bf16
-//             and store.
+//   * warp 0: TMA producer  - A, B and both scale-factor blocks of a 256-wide K slab land in a
+//             ring of shared-memory stages, completion counted on mbarriers;
+//   * warp 1: MMA issuer    - four tcgen05.mma.kind::mxf4nvf4.block_scale (K = 64 each) per
+//             slab, accumulating into TMEM; tcgen05.commit releases the stage;
+//   * warps 2-9: scale warps - two sets of four (one warp per 32-lane quarter of tensor
+//             memory), each set owning the stages of one parity: ld.shared the slab's scale
+//             factors and tcgen05.st them into the stage's tensor-memory columns;
+//   * warps 10-17: epilogue - tcgen05.ld the accumulator (lane quarter x column half), scale by
+//             alpha, convert to bf16, release tensor memory, then either store rows directly or
+//             (CTA-pair variants) write them 128-byte-swizzled into a staging buffer and let the
+//             TMA store 32 x 64 sub-tiles, once per destination buffer.  With several destinations
+//             (this GPU's buffer and the peers' buffers mapped over NVLink) that store is the
+//             output all-gather of a column-sharded projection.
 //
-// With kCtaGroup == 2 two CTAs of a cluster share one 256 x BN tile: each loads its own
-// 128 rows of A and half of B, the leader issues cta_group::2 MMAs for both.  No load
-// uses cluster multicast: every TMA load is unicast into the issuing CTA's own shared
-// memory, and cross-CTA signalling uses the cta_group::2 completion form and plain
-// remote mbarrier arrives.
+// With CG == 2 two CTAs of a cluster share one 256 x BN tile: each loads its own 128 rows of A
+// and half of B, the leader issues cta_group::2 MMAs for both.  No load uses cluster multicast:
+// every TMA load is unicast into the issuing CTA's own shared memory, and cross-CTA signalling
+// uses the cta_group::2 completion form and plain remote mbarrier arrives.  Peer GPUs are only
+// ever written (TMA stores), never read.
 //
 // Every wait is bounded.  A wait that expires records a code in a device status word,
 // raises a CTA-wide abort flag so the other roles drain, and the kernel exits normally
@@ -236,7 +242,7 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
 }
 
 // ---- shared memory ------------------------------------------------------------------------------
-template <int CG, int BN, int STAGES, bool TMA_OUT = false>
+template <int CG, int BN, int STAGES, int TMA_OUT = 0>
 struct SmemLayout {
   static constexpr int kBRows = BN / CG;                       // rows of B held by one CTA
   static constexpr int kChunks = BN / 128 > 0 ? BN / 128 : 1;  // 128-row scale chunks of B
@@ -247,9 +253,11 @@ struct SmemLayout {
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr int kSfCols = 16 + 16 * kChunks;            // TMEM columns of one stage's scales
   static constexpr int kBarrierBytes = 512;
-  // output staging of the TMA-store epilogue: per epilogue warp 32 rows x BN/2 columns of bf16,
-  // cut into 32 x 64 sub-tiles of 4 KB (128-byte rows, 128-byte swizzle)
-  static constexpr int kStagingBytes = TMA_OUT ? kBlockM * BN * 2 : 0;
+  // output staging of the TMA-store epilogue (TMA_OUT > 0): every epilogue warp owns TMA_OUT
+  // sub-tiles of 32 rows x 64 bf16 columns (4 KB, 128-byte rows, 128-byte swizzle) and pushes its
+  // 32 x BN/2 part of the tile through them
+  static constexpr int kStagingBytes = 8 * TMA_OUT * 4096;
+  static_assert(TMA_OUT == 0 || (BN / 2 / 64) % TMA_OUT == 0, "sub-tiles per warp divide its columns");
   static constexpr int kRingBytes = STAGES * kStageBytes + kStagingBytes;
   static constexpr int kTotal = kRingBytes + kBarrierBytes + 1024;  // + alignment slack
   static_assert(kStageBytes % 1024 == 0, "stages and staging stay 1024-byte aligned");
@@ -334,11 +342,11 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-template <int CG, int BN, int STAGES, bool TMA_OUT>
+template <int CG, int BN, int STAGES, int TMA_OUT>
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                      const __grid_constant__ GemmParams p, const __grid_constant__ OutMaps<TMA_OUT> out_maps) {
+                      const __grid_constant__ GemmParams p, const __grid_constant__ OutMaps<(TMA_OUT > 0)> out_maps) {
   using L = SmemLayout<CG, BN, STAGES, TMA_OUT>;
   constexpr int kTmemCols = 512;
   constexpr uint32_t kIdesc = instr_desc(kBlockM * CG, BN);
@@ -580,47 +588,54 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (eprof) { t_body += clock64() - w1; ++n_tiles; }
         continue;
       }
-      if constexpr (TMA_OUT) {
-        // Drain through shared memory: each lane owns one row and writes 16-byte chunks at their
-        // 128-byte-swizzled position (conflict-free), then one lane hands every 32 x 64 sub-tile to
-        // the TMA, once per destination buffer.  Rows past M are clipped by the tensor map.  The
-        // stores run while the next tile is multiplied; peers are reached by stores only.
+      if constexpr (TMA_OUT > 0) {
+        // Drain to registers, hand tensor memory back, then push the rows through shared memory:
+        // each lane owns one row and writes 16-byte chunks at their 128-byte-swizzled position
+        // (conflict-free); one lane hands every 32 x 64 sub-tile to the TMA, once per destination
+        // buffer.  Rows past M are clipped by the tensor map.  The stores run while the next tile is
+        // multiplied; peers are reached by stores only.
+        constexpr int kSubs = kHalf / 64;
         const uint32_t staging = smem_base + STAGES * L::kStageBytes +
-                                 static_cast<uint32_t>(warp - kWarpEpi0) * (kHalf / 64) * 4096u;
-        if (lane == 0) bulk_wait_read_all();  // the previous tile's stores have read the staging
-        __syncwarp();
+                                 static_cast<uint32_t>(warp - kWarpEpi0) * TMA_OUT * 4096u;
+        uint32_t packed[kHalf / 2];
 #pragma unroll
         for (int c0 = 0; c0 < kHalf; c0 += 32) {
           uint32_t v[32];
           tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * kHalf + c0, v);
           tmem_ld_wait();
-          const uint32_t sub = staging + (c0 / 64) * 4096u + lane * 128u;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t w[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              w[i] = pack_from_f32<BF16Tag>(__uint_as_float(v[8 * j + 2 * i]) * alpha,
-                                            __uint_as_float(v[8 * j + 2 * i + 1]) * alpha);
-            const uint32_t chunk = static_cast<uint32_t>((c0 % 64) / 8 + j) ^ (lane & 7u);
-            sts128(sub + chunk * 16u, w[0], w[1], w[2], w[3]);
-          }
+          for (int i = 0; i < 16; ++i)
+            packed[c0 / 2 + i] = pack_from_f32<BF16Tag>(__uint_as_float(v[2 * i]) * alpha,
+                                                        __uint_as_float(v[2 * i + 1]) * alpha);
         }
         tc_fence_before();
-        fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
           if (leader) mbar_arrive_local(tmem_empty_bar);
           else mbar_arrive_cluster_relaxed(empty_target);
-          const int row0 = (tm * CG + static_cast<int>(rank)) * kBlockM + quarter * 32;
-          if (row0 < p.M) {
-            const int x0 = p.col0 + tn * BN + half * kHalf;
-            for (int d = 0; d < p.n_dest; ++d)
+        }
+        const int row0 = (tm * CG + static_cast<int>(rank)) * kBlockM + quarter * 32;
+        const int x0 = p.col0 + tn * BN + half * kHalf;
 #pragma unroll
-              for (int sub = 0; sub < kHalf / 64; ++sub)
-                tma_store_2d(&out_maps.m[d], staging + sub * 4096u, x0 + sub * 64, row0);
+        for (int sub = 0; sub < kSubs; ++sub) {
+          if (sub % TMA_OUT == 0) {
+            if (lane == 0) bulk_wait_read_all();  // earlier stores have read the staging
+            __syncwarp();
           }
-          bulk_commit();
+          const uint32_t buf = staging + (sub % TMA_OUT) * 4096u;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t chunk = static_cast<uint32_t>(j) ^ (lane & 7u);
+            sts128(buf + lane * 128u + chunk * 16u, packed[sub * 32 + 4 * j], packed[sub * 32 + 4 * j + 1],
+                   packed[sub * 32 + 4 * j + 2], packed[sub * 32 + 4 * j + 3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (row0 < p.M)
+              for (int d = 0; d < p.n_dest; ++d) tma_store_2d(&out_maps.m[d], buf, x0 + sub * 64, row0);
+            bulk_commit();
+          }
         }
       } else {
       uint32_t packed[kHalf / 2];
@@ -650,7 +665,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       acc_phase ^= 1u;
       if (eprof) { t_body += clock64() - w1; ++n_tiles; }
     }
-    if constexpr (TMA_OUT) {
+    if constexpr (TMA_OUT > 0) {
       if (lane == 0) bulk_wait_all();  // every store has left shared memory and is written
     }
     if (eprof) {
@@ -836,10 +851,10 @@ int encode_output_map(CUtensorMap* map, void* base, int M, int ldd) {
   return B2_OK;
 }
 
-template <int CG, int BN, int STAGES, bool TMA_OUT = false>
+template <int CG, int BN, int STAGES, int TMA_OUT = 0>
 int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N, int K, int splits,
                    uint32_t* status, float* partial, cudaStream_t stream, const GatherTarget& gather = GatherTarget(),
-                   const OutMaps<TMA_OUT>& out_maps = OutMaps<TMA_OUT>()) {
+                   const OutMaps<(TMA_OUT > 0)>& out_maps = OutMaps<(TMA_OUT > 0)>()) {
   using L = SmemLayout<CG, BN, STAGES, TMA_OUT>;
   auto kernel = nvfp4_gemm_kernel<CG, BN, STAGES, TMA_OUT>;
   GemmParams p;
@@ -929,7 +944,7 @@ int choose_splits(int tiles, int k_slabs, int units_available) {
   return splits;
 }
 
-template <int CG, int BN, int STAGES, bool TMA_OUT = false>
+template <int CG, int BN, int STAGES, int TMA_OUT = 0>
 int launch_variant(const void* A, const void* B, const void* SFA, const void* SFB, const float* alpha,
                    void* D, int M, int N, int K, int variant, cudaStream_t stream) {
   uint32_t* status = nullptr;
@@ -955,7 +970,7 @@ int launch_variant(const void* A, const void* B, const void* SFA, const void* SF
   if (splits > 1) {
     if (int rc = partial_scratch(static_cast<size_t>(splits) * M * N * sizeof(float), &partial)) return rc;
   }
-  if constexpr (TMA_OUT) {
+  if constexpr (TMA_OUT > 0) {
     OutMaps<true> out_maps;
     {
       const MapKey key{D, nullptr, nullptr, nullptr, M, N, 0, -1};
@@ -970,7 +985,7 @@ int launch_variant(const void* A, const void* B, const void* SFA, const void* SF
     }
     GatherTarget target;
     target.n_dest = 1;
-    return launch_kernels<CG, BN, STAGES, true>(maps, alpha, D, M, N, K, splits, status, partial, stream, target,
+    return launch_kernels<CG, BN, STAGES, TMA_OUT>(maps, alpha, D, M, N, K, splits, status, partial, stream, target,
                                                 out_maps);
   } else {
     return launch_kernels<CG, BN, STAGES>(maps, alpha, D, M, N, K, splits, status, partial, stream);
@@ -1030,8 +1045,8 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
   switch (variant) {
     case 0: return launch_variant<1, 128, 6>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 0, s);
     case 1: return launch_variant<1, 256, 4>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 1, s);
-    case 2: return launch_variant<2, 256, 4, true>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 2, s);
-    default: return launch_variant<2, 128, 6, true>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
+    case 2: return launch_variant<2, 256, 5, 1>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 2, s);
+    default: return launch_variant<2, 128, 6, 1>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
   }
 }
 
@@ -1270,11 +1285,11 @@ extern "C" int b2_nvfp4_gemm_allgather(const void* A, const void* B, const void*
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   MapSet maps;
   if (N % 256 == 0) {
-    if (int rc = encode_maps<2, 256, 4>(&maps, A, B, SFA, SFB, M, N, K)) return rc;
-    return launch_kernels<2, 256, 4, true>(maps, alpha_dev, D_all[rank], M, N, K, 1, status, nullptr, s, gather,
+    if (int rc = encode_maps<2, 256, 5>(&maps, A, B, SFA, SFB, M, N, K)) return rc;
+    return launch_kernels<2, 256, 5, 1>(maps, alpha_dev, D_all[rank], M, N, K, 1, status, nullptr, s, gather,
                                            out_maps);
   }
   if (int rc = encode_maps<2, 128, 6>(&maps, A, B, SFA, SFB, M, N, K)) return rc;
-  return launch_kernels<2, 128, 6, true>(maps, alpha_dev, D_all[rank], M, N, K, 1, status, nullptr, s, gather,
+  return launch_kernels<2, 128, 6, 1>(maps, alpha_dev, D_all[rank], M, N, K, 1, status, nullptr, s, gather,
                                          out_maps);
 }
