@@ -199,6 +199,107 @@ __global__ void __launch_bounds__(TPR == 256 ? 256 : 128)
   if (p.enable_pdl) pdl_launch_dependents();
 }
 
+// Register-resident variant for rows that split evenly over the virtual threads
+// (H / 8 == vb * TPR, vb <= VBMAX, TPR >= 32): thread t keeps its chunks t, t + TPR, ... in
+// registers from the single HBM read, adds their squares in the reference's order, and later
+// quantizes the very same chunks, so the row never visits shared memory.  A scale block is 2 (or
+// 4) consecutive chunks, which sit in adjacent lanes: the block maximum is combined with one (two)
+// XOR shuffles of the packed pair maximum, each lane derives the same scale and quantizes its own
+// eight values to one 32-bit word, and the first lane of a block stores the scale byte.
+template <typename Tag, int TPR, int BLOCK, int VBMAX>
+__global__ void __launch_bounds__(TPR == 256 ? 256 : 128)
+    rmsnorm_fp4quant_reg_kernel(const __grid_constant__ RmsParams p) {
+  constexpr int kThreads = TPR == 256 ? 256 : 128;
+  constexpr int kRows = kThreads / TPR;
+  constexpr int kWarpsPerRow = TPR / 32;
+  constexpr int kLanesPerBlock = BLOCK / 8;
+  __shared__ float red[kRows * kWarpsPerRow];
+
+  const int tid = threadIdx.x;
+  const int row_in_cta = tid / TPR;
+  const int t = tid % TPR;
+  const int row = blockIdx.x * kRows + row_in_cta;
+  const bool row_valid = row < p.M;  // uniform within a warp: a warp never spans two rows
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+
+  if (p.enable_pdl) pdl_wait();
+
+  const float rcp6 = rcp_approx_ftz(6.0f);
+  const uint4* xrow = reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(row) * p.H * 2);
+  uint4 c[VBMAX];
+#pragma unroll
+  for (int b = 0; b < VBMAX; ++b) {
+    if (row_valid && b < p.vb) {
+      uint32_t r[4];
+      ld_stream_128(xrow + t + b * TPR, r);
+      c[b] = make_uint4(r[0], r[1], r[2], r[3]);
+    } else {
+      c[b] = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  float sum = 0.0f;
+#pragma unroll
+  for (int b = 0; b < VBMAX; ++b)
+    if (b < p.vb) sum = sum_sq_8<Tag>(sum, c[b]);
+#pragma unroll
+  for (int x = 1; x < 32; x <<= 1) sum = add_f32(sum, __shfl_xor_sync(0xFFFFFFFFu, sum, x));
+  if constexpr (kWarpsPerRow > 1) {
+    const int row_warp = warp / kWarpsPerRow;
+    const int warp_in_row = warp % kWarpsPerRow;
+    if (lane == 0) red[row_warp + warp_in_row * kRows] = sum;
+    __syncthreads();
+    float part = lane < kWarpsPerRow ? red[row_warp + lane * kRows] : 0.0f;
+#pragma unroll
+    for (int x = 1; x < 32; x <<= 1) part = add_f32(part, __shfl_xor_sync(0xFFFFFFFFu, part, x));
+    sum = part;
+  }
+  if (!row_valid) return;
+  const float shifted =
+      p.pow2 ? __fmaf_rn(sum, p.inv_h, p.eps) : add_f32(__fdiv_rn(sum, static_cast<float>(p.H)), p.eps);
+  const float rstd = rsqrt_approx_ftz(shifted);
+  const float gs = p.use_e4m3 ? *p.gs : 0.0f;
+
+  const uint4* wrow = reinterpret_cast<const uint4*>(p.w);
+  uint32_t* yrow = reinterpret_cast<uint32_t*>(p.y + static_cast<int64_t>(row) * (p.H >> 1));
+  const int64_t sf_row = p.swizzled ? sf_offset_128x4(row, 0, p.sf_pad_cols) : static_cast<int64_t>(row) * p.sf_cols;
+  uint8_t* sf_base = p.sf + sf_row;
+#pragma unroll
+  for (int b = 0; b < VBMAX; ++b) {
+    if (b < p.vb) {
+      const int chunk = t + b * TPR;
+      const uint4 wc = __ldg(wrow + chunk);
+      uint32_t prod[4];
+      prod[0] = hmul2<Tag>(c[b].x, wc.x);
+      prod[1] = hmul2<Tag>(c[b].y, wc.y);
+      prod[2] = hmul2<Tag>(c[b].z, wc.z);
+      prod[3] = hmul2<Tag>(c[b].w, wc.w);
+      uint32_t m2 = absmax_4<Tag>(prod);
+      m2 = hmax2<Tag>(m2, __shfl_xor_sync(0xFFFFFFFFu, m2, 1));
+      if constexpr (kLanesPerBlock == 4) m2 = hmax2<Tag>(m2, __shfl_xor_sync(0xFFFFFFFFu, m2, 2));
+      const float max_abs = mul_f32(pair_max_to_f32<Tag>(m2), rstd);
+      uint32_t code;
+      float out_scale;
+      if (p.use_e4m3) {
+        const float s = min_f32(mul_f32(mul_f32(gs, max_abs), rcp6), 448.0f);
+        code = cvt_f32_to_e4m3(s) & 0xFFu;
+        const float d = e4m3_to_f32(code);
+        const float r = rcp_approx_ftz(d);
+        out_scale = mul_f32(d == 0.0f ? 0.0f : r, gs);
+      } else {
+        code = cvt_f32_to_ue8m0(mul_f32(max_abs, rcp6));
+        out_scale = ue8m0_to_output_scale(code);
+      }
+      yrow[chunk] = quantize_8<Tag>(prod, rstd, out_scale);
+      if ((t & (kLanesPerBlock - 1)) == 0) {
+        const int j = chunk / kLanesPerBlock;
+        sf_base[p.swizzled ? ((j >> 2) * 512 + (j & 3)) : j] = static_cast<uint8_t>(code);
+      }
+    }
+  }
+  if (p.enable_pdl) pdl_launch_dependents();
+}
+
 // rmsnorm_fp4quant.py _threads_per_row :344-355
 int threads_per_row(int h) {
   if (h <= 64) return 8;
@@ -209,11 +310,35 @@ int threads_per_row(int h) {
   return 256;
 }
 
+template <typename Kernel>
+int launch_config(Kernel kernel, const RmsParams& p, int rows_per_cta, int threads, size_t smem, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((p.M + rows_per_cta - 1) / rows_per_cta);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (p.enable_pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p));
+  return B2_OK;
+}
+
 template <typename Tag, int TPR, int BLOCK>
 int launch(const RmsParams& p, cudaStream_t stream) {
   constexpr int kThreads = TPR == 256 ? 256 : 128;
   constexpr int kRows = kThreads / TPR;
   constexpr int kWarpsPerRow = TPR >= 32 ? TPR / 32 : 1;
+  if constexpr (TPR >= 32) {
+    if ((p.H >> 3) == p.vb * TPR && p.vb <= 16) {
+      if (p.vb <= 8) return launch_config(rmsnorm_fp4quant_reg_kernel<Tag, TPR, BLOCK, 8>, p, kRows, kThreads, 0, stream);
+      return launch_config(rmsnorm_fp4quant_reg_kernel<Tag, TPR, BLOCK, 16>, p, kRows, kThreads, 0, stream);
+    }
+  }
   auto kernel = rmsnorm_fp4quant_kernel<Tag, TPR, BLOCK>;
   const size_t smem = static_cast<size_t>(kRows) * p.vb * TPR * 16 + kRows * kWarpsPerRow * 4;
   if (smem > 48 * 1024) {
