@@ -31,20 +31,30 @@ def _selected():
     return picked
 
 
-CLUSTER_CASES = ("cluster2", "cluster16")
-
-
 @pytest.mark.parametrize("config", _selected(), ids=lambda c: c["label"])
 def test_reference_config_is_bit_exact(config, oracle_expected):
     from tirx_kernels.registry import discover_kernels
     from tirx_kernels.runner import run_kernel_test
 
     kernels = discover_kernels()
-    if config["case"] in CLUSTER_CASES:
-        with pytest.raises(ValueError, match="cluster reduction"):
-            run_kernel_test("flashinfer_rmsnorm_fp4quant", config, registry=kernels)
-        return
     run_kernel_test("flashinfer_rmsnorm_fp4quant", config, registry=kernels)
+
+
+@pytest.mark.parametrize("kwargs", [
+    dict(dtype="float16", H=131072, M=3, block_size=32, scale_format="ue8m0", swizzled=True, global_scale_mode="none"),
+    dict(dtype="bfloat16", H=65536, M=130, swizzled=True),
+    dict(dtype="bfloat16", H=98304, M=2),
+], ids=lambda k: f"{k['dtype']}_h{k['H']}_m{k['M']}")
+def test_rows_spread_over_a_cluster_are_bit_exact(kwargs, oracle_expected):
+    """Rows too wide for one CTA (the reference's cluster path) beyond its two structural configs:
+    several rows per launch, both block formats, a row length that is not a power of two."""
+    from tirx_kernels.registry import discover_kernels
+    from tirx_kernels.runner import run_kernel_test
+
+    mod = _module()
+    kwargs = dict(kwargs)
+    config = mod._cfg("cluster_extra", kwargs.pop("dtype"), kwargs.pop("H"), **kwargs)
+    run_kernel_test("flashinfer_rmsnorm_fp4quant", config, registry=discover_kernels())
 
 
 def test_baseline_shape_is_bit_exact_at_full_size(native):

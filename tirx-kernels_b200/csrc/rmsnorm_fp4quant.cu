@@ -300,6 +300,178 @@ __global__ void __launch_bounds__(TPR == 256 ? 256 : 128)
   if (p.enable_pdl) pdl_launch_dependents();
 }
 
+// ---- rows spread over a thread-block cluster (rmsnorm_fp4quant.py kernel_body :857-891) ----------
+// When one CTA cannot hold a row, the reference gives CTA c of a cluster the columns
+// [c * cols, (c + 1) * cols), lets every warp of every CTA publish its partial sum at index
+// c * warps_per_row + warp in all CTAs of the cluster, and has each lane add partials lane,
+// lane + 32, ... before the final butterfly.  Same here: 256 threads per CTA, one row per cluster,
+// partials written into every CTA's shared memory through distributed shared memory, one
+// hardware cluster barrier, then the quantization pass over this CTA's own columns.
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(const float* local, uint32_t target_cta, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote)
+               : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(local))), "r"(target_cta));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <typename Tag, int BLOCK>
+__global__ void __launch_bounds__(256) rmsnorm_fp4quant_cluster_kernel(const __grid_constant__ RmsParams p, int cluster_n) {
+  constexpr int kTpr = 256, kWarps = 8;
+  constexpr int kChunksPerBlock = BLOCK / 8;
+  extern __shared__ __align__(16) uint8_t smem[];
+  uint4* tile = reinterpret_cast<uint4*>(smem);  // this CTA's vb * 256 chunks
+  float* partials = reinterpret_cast<float*>(smem + static_cast<size_t>(p.vb) * kTpr * 16);  // [cluster_n * 8]
+
+  const int t = threadIdx.x;
+  const int lane = t & 31, warp = t >> 5;
+  const int cta = static_cast<int>(cluster_rank());
+  const int row = blockIdx.x / cluster_n;  // < M by construction of the grid
+  const int nchunks = p.H >> 3;
+  const int chunk0 = cta * p.vb * kTpr;  // first chunk of this CTA's column range
+
+  if (p.enable_pdl) pdl_wait();
+  const float rcp6 = rcp_approx_ftz(6.0f);
+  const uint4* xrow = reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(row) * p.H * 2);
+
+  float sum = 0.0f;
+  for (int b0 = 0; b0 < p.vb; b0 += 4) {
+    uint4 c[4];
+    bool ok[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int local = t + (b0 + j) * kTpr;
+      ok[j] = (b0 + j) < p.vb && chunk0 + local < nchunks;
+      if (ok[j]) {
+        uint32_t r[4];
+        ld_stream_128(xrow + chunk0 + local, r);
+        c[j] = make_uint4(r[0], r[1], r[2], r[3]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (ok[j]) {
+        tile[t + (b0 + j) * kTpr] = c[j];
+        sum = sum_sq_8<Tag>(sum, c[j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int x = 1; x < 32; x <<= 1) sum = add_f32(sum, __shfl_xor_sync(0xFFFFFFFFu, sum, x));
+  if (lane < cluster_n) st_cluster_f32(partials + cta * kWarps + warp, static_cast<uint32_t>(lane), sum);
+  cluster_barrier();  // every partial of the row is in this CTA's shared memory; also orders `tile`
+  const int total = cluster_n * kWarps;
+  float part = 0.0f;
+  for (int i = lane; i < total; i += 32) part = add_f32(part, partials[i]);
+#pragma unroll
+  for (int x = 1; x < 32; x <<= 1) part = add_f32(part, __shfl_xor_sync(0xFFFFFFFFu, part, x));
+  const float shifted =
+      p.pow2 ? __fmaf_rn(part, p.inv_h, p.eps) : add_f32(__fdiv_rn(part, static_cast<float>(p.H)), p.eps);
+  const float rstd = rsqrt_approx_ftz(shifted);
+  const float gs = p.use_e4m3 ? *p.gs : 0.0f;
+
+  const uint4* wrow = reinterpret_cast<const uint4*>(p.w);
+  uint8_t* yrow = p.y + static_cast<int64_t>(row) * (p.H >> 1);
+  const int64_t sf_row = p.swizzled ? sf_offset_128x4(row, 0, p.sf_pad_cols) : static_cast<int64_t>(row) * p.sf_cols;
+  uint8_t* sf_base = p.sf + sf_row;
+  const int blocks_here = p.vb * kTpr / kChunksPerBlock;
+  const int block0 = chunk0 / kChunksPerBlock;
+  for (int jl = t; jl < blocks_here; jl += kTpr) {
+    const int j = block0 + jl;
+    if (j >= p.sf_cols) break;
+    uint32_t prod[kChunksPerBlock][4];
+#pragma unroll
+    for (int c = 0; c < kChunksPerBlock; ++c) {
+      const uint4 xc = tile[jl * kChunksPerBlock + c];
+      const uint4 wc = __ldg(wrow + j * kChunksPerBlock + c);
+      prod[c][0] = hmul2<Tag>(xc.x, wc.x);
+      prod[c][1] = hmul2<Tag>(xc.y, wc.y);
+      prod[c][2] = hmul2<Tag>(xc.z, wc.z);
+      prod[c][3] = hmul2<Tag>(xc.w, wc.w);
+    }
+    uint32_t m2 = absmax_4<Tag>(prod[0]);
+#pragma unroll
+    for (int c = 1; c < kChunksPerBlock; ++c) m2 = hmax2<Tag>(m2, absmax_4<Tag>(prod[c]));
+    const float max_abs = mul_f32(pair_max_to_f32<Tag>(m2), rstd);
+    uint32_t code;
+    float out_scale;
+    if (p.use_e4m3) {
+      const float sc = min_f32(mul_f32(mul_f32(gs, max_abs), rcp6), 448.0f);
+      code = cvt_f32_to_e4m3(sc) & 0xFFu;
+      const float d = e4m3_to_f32(code);
+      const float r = rcp_approx_ftz(d);
+      out_scale = mul_f32(d == 0.0f ? 0.0f : r, gs);
+    } else {
+      code = cvt_f32_to_ue8m0(mul_f32(max_abs, rcp6));
+      out_scale = ue8m0_to_output_scale(code);
+    }
+    uint32_t q[kChunksPerBlock];
+#pragma unroll
+    for (int c = 0; c < kChunksPerBlock; ++c) q[c] = quantize_8<Tag>(prod[c], rstd, out_scale);
+    if constexpr (kChunksPerBlock == 2) {
+      *reinterpret_cast<uint2*>(yrow + j * 8) = make_uint2(q[0], q[1]);
+    } else {
+      *reinterpret_cast<uint4*>(yrow + j * 16) = make_uint4(q[0], q[1], q[2], q[3]);
+    }
+    sf_base[p.swizzled ? ((j >> 2) * 512 + (j & 3)) : j] = static_cast<uint8_t>(code);
+  }
+  if (p.enable_pdl) pdl_launch_dependents();
+}
+
+template <typename Tag, int BLOCK>
+int launch_cluster(const RmsParams& p, int cluster_n, cudaStream_t stream) {
+  auto kernel = rmsnorm_fp4quant_cluster_kernel<Tag, BLOCK>;
+  const size_t smem = static_cast<size_t>(p.vb) * 256 * 16 + static_cast<size_t>(cluster_n) * 8 * 4;
+  B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  if (cluster_n > 8) B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.M) * cluster_n);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster_n;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.numAttrs = 1;
+  if (p.enable_pdl) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
+  cfg.attrs = attr;
+  B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, cluster_n));
+  return B2_OK;
+}
+
+// rmsnorm_fp4quant.py _derived_config / _estimate_smem / _source_config :358-400: the smallest
+// cluster size whose per-CTA row tile fits in shared memory.
+int threads_per_row(int h);
+int source_cluster_n(int H) {
+  for (int cand = 1; cand <= 16; cand *= 2) {
+    const int hpc = H / cand;
+    const int tpr = threads_per_row(hpc);
+    const int threads = hpc <= 16384 ? 128 : 256;
+    const int rows = threads / tpr;
+    const int wpr = std::max(tpr / 32, 1);
+    const int64_t vb = std::max(1, ((hpc / 8) + tpr - 1) / tpr);
+    const int64_t tile = static_cast<int64_t>(rows) * 8 * vb * tpr * 2;
+    const int64_t red = static_cast<int64_t>(rows) * wpr * 4;
+    const int64_t est = cand == 1 ? 2 * tile + red : tile + red * cand + 8;
+    if (H % cand == 0 && est <= 232448) return cand;
+  }
+  return 16;
+}
+
 // rmsnorm_fp4quant.py _threads_per_row :344-355
 int threads_per_row(int h) {
   if (h <= 64) return 8;
@@ -435,14 +607,24 @@ extern "C" int b2_rmsnorm_fp4quant(const void* x, const void* w, void* y, void* 
   p.eps = eps;
   p.inv_h = 1.0f / static_cast<float>(H);
   p.enable_pdl = enable_pdl ? 1 : 0;
-  // Rows that the reference splits over a thread-block cluster (one CTA cannot hold
-  // the row in shared memory) use a different reduction tree; not built yet.
-  const size_t tile_bytes = static_cast<size_t>(p.vb) * tpr * 16 * ((tpr == 256 ? 256 : 128) / tpr);
-  if (2 * tile_bytes + 64 > 232448) {
-    set_error("b2_rmsnorm_fp4quant: H=%d needs the cluster reduction path, which is not built", H);
-    return B2_ERR_UNSUPPORTED;
-  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int cluster_n = source_cluster_n(H);
+  if (cluster_n > 1) {
+    // one CTA cannot hold the row: spread it over a cluster, as the reference does
+    const int hpc = H / cluster_n;
+    if (threads_per_row(hpc) != 256) {
+      set_error("b2_rmsnorm_fp4quant: H=%d: unexpected cluster configuration", H);
+      return B2_ERR_UNSUPPORTED;
+    }
+    p.vb = std::max(1, ((hpc / 8) + 255) / 256);
+    if (static_cast<size_t>(p.vb) * 256 * 16 + 1024 > 232448 || static_cast<int64_t>(M) * cluster_n > 2147483647ll) {
+      set_error("b2_rmsnorm_fp4quant: H=%d does not fit a cluster of 16 CTAs", H);
+      return B2_ERR_UNSUPPORTED;
+    }
+    if (in_dtype == B2_DTYPE_F16)
+      return block_size == 16 ? launch_cluster<F16Tag, 16>(p, cluster_n, s) : launch_cluster<F16Tag, 32>(p, cluster_n, s);
+    return block_size == 16 ? launch_cluster<BF16Tag, 16>(p, cluster_n, s) : launch_cluster<BF16Tag, 32>(p, cluster_n, s);
+  }
   if (in_dtype == B2_DTYPE_F16) return dispatch_block<F16Tag>(p, tpr, s);
   return dispatch_block<BF16Tag>(p, tpr, s);
 }
