@@ -92,6 +92,23 @@ int b2_rmsnorm_fp4quant(const void* x, const void* w, void* y, void* sf, const f
                         int swizzled, int enable_pdl, void* stream);
 
 /*
+ * Residual add + RMSNorm + FP4 block quantization: the executable of
+ * tirx_kernels/flashinfer/norm/add_rmsnorm_fp4quant.py:1210-1221 (ABI x, residual, weight, y, scale,
+ * scale_unswizzled, y_norm, global_scale, M, eps), called by _launch_tirx :1457-1470; the compile-time
+ * knobs of get_kernel :788-799 are arguments here.
+ *   residual  in: residual [M, H]; out: x + residual rounded to the input dtype (in place)
+ *   sf        scale bytes, 128x4-swizzled when `swizzled` or `output_both_sf_layouts`, else [M, H/block]
+ *   sf_unswizzled  second, linear copy of the scale bytes when `output_both_sf_layouts` (else unused, may be NULL)
+ *   y_norm    the normalized, weighted row in the input dtype when `output_norm` (else unused, may be NULL)
+ * Other arguments as b2_rmsnorm_fp4quant.  Rows with H >= 32768 are spread over a thread-block
+ * cluster exactly where the reference does (_source_config :354-363), which fixes the summation order.
+ */
+int b2_add_rmsnorm_fp4quant(const void* x, void* residual, const void* w, void* y, void* sf,
+                            void* sf_unswizzled, void* y_norm, const float* gs_dev, int M, int H,
+                            float eps, int in_dtype, int block_size, int scale_format, int swizzled,
+                            int output_both_sf_layouts, int output_norm, int enable_pdl, void* stream);
+
+/*
  * Dense block-scaled NVFP4 GEMM:  D[M,N] (bf16) = alpha * A[M,K] * B[N,K]^T.
  *
  * Replaces _Runner.__call__ in tirx_kernels/basic/nvfp4_gemm.py:985-997 (kernel

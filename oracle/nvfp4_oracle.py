@@ -362,8 +362,12 @@ def _butterfly(v: np.ndarray, xors) -> np.ndarray:
 def rmsnorm_sum_of_squares(x_bits, dtype: str) -> np.ndarray:
     """The reference's fp32 reduction tree, kernel_body :786-893; returns [M] float32."""
     x = bits_to_f32(x_bits, dtype)
+    return sum_of_squares_tree(x, source_config(x.shape[1]))
+
+
+def sum_of_squares_tree(x: np.ndarray, cfg: dict) -> np.ndarray:
+    """Sum of x*x over the rows of fp32 `x` [M, H] in the order a launch configuration fixes."""
     M, H = x.shape
-    cfg = source_config(H)
     tpr, vb, cols, cn = cfg["tpr"], cfg["vec_blocks"], cfg["cols"], cfg["cluster_n"]
     wpr = cfg["warps_per_row"]
     padded = np.zeros((M, cn * cols), dtype=np.float32)
@@ -455,6 +459,108 @@ def rmsnorm_fp4quant(x_bits, w_bits, dtype: str, global_scale, eps: float, block
     sf = np.full(-(-M // 128) * 128 * pad_cols, sf_fill, dtype=np.uint8)
     sf[sf_offsets("128x4", np.arange(M)[:, None], np.arange(nblk)[None, :], pad_cols)] = code
     return packed, sf
+
+
+# --------------------------------------------------------------------------------------
+# flashinfer_add_rmsnorm_fp4quant  (tirx_kernels/flashinfer/norm/add_rmsnorm_fp4quant.py)
+# --------------------------------------------------------------------------------------
+def add_source_config(H: int) -> dict:
+    """_derived_config / _estimate_smem / _source_config :325-363: as `source_config`, but the
+    one-CTA form keeps four row tiles (x, residual, weight, h) and the cluster form two."""
+
+    def derived(cluster_n):
+        hpc = H // cluster_n
+        tpr = threads_per_row(hpc)
+        threads = 128 if hpc <= 16384 else 256
+        rows = threads // tpr
+        wpr = max(tpr // 32, 1)
+        vb = max(1, -(-(hpc // 8) // tpr))
+        cols = 8 * vb * tpr
+        return dict(tpr=tpr, threads=threads, rows=rows, warps_per_row=wpr, vec_blocks=vb, cols=cols,
+                    tile_bytes=rows * cols * 2)
+
+    cluster_n = 16
+    for cand in (1, 2, 4, 8, 16):
+        c = derived(cand)
+        red = c["rows"] * c["warps_per_row"] * 4
+        est = 4 * c["tile_bytes"] + red if cand == 1 else 2 * c["tile_bytes"] + red * cand + 8
+        if H % cand == 0 and est <= 232448:
+            cluster_n = cand
+            break
+    cfg = derived(cluster_n)
+    cfg["cluster_n"] = cluster_n
+    return cfg
+
+
+def add_rmsnorm_fp4quant(x_bits, r_bits, w_bits, dtype: str, global_scale, eps: float, block_size: int = 16,
+                         scale_format: str = "e4m3", swizzled: bool = False, mufu=None, sf_fill: int = 0):
+    """kernel_body :825-1206 with _process_add_scale_block :156-314.
+
+    h = x + residual in fp32 (add.f32x2 :951-958); the squares of the UNROUNDED sums are added in the
+    usual tree order (:960-983); h rounded to the input dtype replaces the residual (:1052-1071).
+    One CTA per row (:177-229): value = (h * rstd) * w in fp32 on the rounded h, block maximum of
+    |value| in fp32.  Cluster rows (:230-258): the rmsnorm_fp4quant recipe on the rounded h
+    (16-bit product h*w, maximum times rstd).  Scale and output scale as in rmsnorm_fp4quant.
+
+    Returns dict(y, scale (linear [M, nblk] codes), scale_buffer (layout of `swizzled`), y_norm bits
+    (the values before the output scale, rounded to the input dtype :134-153), residual bits).
+    """
+    mufu = mufu or ExactMufu()
+    x_bits = np.asarray(x_bits, dtype=np.uint16)
+    r_bits = np.asarray(r_bits, dtype=np.uint16)
+    w_bits = np.asarray(w_bits, dtype=np.uint16)
+    M, H = x_bits.shape
+    use_e4m3 = block_size == 16 or scale_format == "e4m3"
+    cfg = add_source_config(H)
+    with np.errstate(over="ignore", invalid="ignore"):
+        h32 = (bits_to_f32(x_bits, dtype) + bits_to_f32(r_bits, dtype)).astype(np.float32)
+    h_bits = f32_to_bits(h32, dtype)
+    sum_sq = sum_of_squares_tree(h32, cfg)
+    rstd = mufu.rsqrt_ftz(rmsnorm_shifted_mean(sum_sq, H, eps))[:, None, None]
+    nblk = H // block_size
+    if cfg["cluster_n"] == 1:
+        h = bits_to_f32(h_bits, dtype).reshape(M, nblk, block_size)
+        w = bits_to_f32(w_bits, dtype).reshape(1, nblk, block_size)
+        with np.errstate(over="ignore", invalid="ignore"):
+            values = ((h * rstd).astype(np.float32) * w).astype(np.float32)
+            max_abs = np.fmax.reduce(np.abs(values), axis=-1).astype(np.float32)[..., None]
+    else:
+        prod = mul_16bit(h_bits, w_bits[None, :], dtype).reshape(M, nblk, block_size)
+        with np.errstate(over="ignore", invalid="ignore"):
+            max_xw = np.fmax.reduce(np.abs(prod), axis=-1).astype(np.float32)[..., None]
+            values = (prod * rstd).astype(np.float32)
+            max_abs = (max_xw * rstd).astype(np.float32)
+    rcp6 = mufu.rcp_ftz(np.array([6.0], dtype=np.float32))[0]
+    if use_e4m3:
+        gs = np.float32(global_scale)
+        with np.errstate(over="ignore", invalid="ignore"):
+            sc = ((gs * max_abs).astype(np.float32) * rcp6).astype(np.float32)
+        sc = np.fmin(sc, np.float32(448.0))
+        code = e4m3_encode(sc)
+        d = e4m3_decode(code)
+        r = np.where(d == 0.0, np.float32(0.0), mufu.rcp_ftz(d)).astype(np.float32)
+        with np.errstate(over="ignore", invalid="ignore"):
+            out_scale = (r * gs).astype(np.float32)
+    else:
+        with np.errstate(over="ignore", invalid="ignore"):
+            v = (max_abs * rcp6).astype(np.float32)
+        lg = mufu.lg2(np.where(v > 0, v, np.float32(1.0)))
+        e = np.ceil(lg.astype(np.float64)).astype(np.int64) + 127
+        code = np.where(v <= 0, 0, np.clip(e, 0, 255)).astype(np.uint8)
+        cand = mufu.ex2((127 - code.astype(np.int32)).astype(np.float32))
+        out_scale = np.where(code == 0, np.float32(0.0), cand).astype(np.float32)
+    with np.errstate(over="ignore", invalid="ignore"):
+        scaled = (values * out_scale).astype(np.float32)
+    packed = pack_nibbles(e2m1_encode(scaled).reshape(M, H))
+    code = code.reshape(M, nblk)
+    if swizzled:
+        pad_cols = padded_sf_cols(nblk)
+        buf = np.full(-(-M // 128) * 128 * pad_cols, sf_fill, dtype=np.uint8)
+        buf[sf_offsets("128x4", np.arange(M)[:, None], np.arange(nblk)[None, :], pad_cols)] = code
+    else:
+        buf = code.copy()
+    return {"y": packed, "scale": code.copy(), "scale_buffer": buf,
+            "y_norm": f32_to_bits(values.reshape(M, H), dtype), "residual": h_bits}
 
 
 # --------------------------------------------------------------------------------------

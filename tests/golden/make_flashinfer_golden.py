@@ -5,7 +5,8 @@
 The reference's tests take their expected bytes from flashinfer at test time
 (`flashinfer.quantization.nvfp4_quantize(backend="cute-dsl")`,
 tirx_kernels/flashinfer/quantization/nvfp4_quantize.py:418-438, and
-`flashinfer.cute_dsl.rmsnorm_fp4quant`, tirx_kernels/flashinfer/norm/rmsnorm_fp4quant.py:1187-1215)
+`flashinfer.cute_dsl.rmsnorm_fp4quant`, tirx_kernels/flashinfer/norm/rmsnorm_fp4quant.py:1187-1215,
+`flashinfer.norm.add_rmsnorm_fp4quant`, tirx_kernels/flashinfer/norm/add_rmsnorm_fp4quant.py:1508-1555)
 and store none.  This script runs the flashinfer build installed in this image (0.6.11, not the
 revision the reference pins) on seeded inputs drawn on the CPU and stores its OUTPUTS as small
 .npz files (inputs are regenerated from the seed by `quant_inputs` / `rms_inputs`; their SHA-256
@@ -48,6 +49,15 @@ RMS_CASES = [
     ("bfloat16", 8, 2048, 32, "ue8m0", False, None),
     ("float16", 3, 3088, 16, "e4m3", False, 3.25),
 ]
+ADD_CASES = [
+    # (dtype, M, H, block, scale_format, swizzled, both_layouts, global_scale)
+    ("bfloat16", 5, 4096, 16, "e4m3", True, False, None),
+    ("float16", 7, 1536, 16, "e4m3", False, True, 3.25),
+    ("bfloat16", 4, 2048, 32, "ue8m0", False, False, None),
+    ("bfloat16", 1, 32768, 16, "e4m3", False, False, None),   # the reference spreads this row over two CTAs
+    ("bfloat16", 3, 7168, 16, "e4m3", True, False, None),
+    ("float16", 17, 64, 16, "e4m3", False, False, None),
+]
 
 
 def bits(t):
@@ -80,6 +90,31 @@ def rms_inputs(case):
     x = torch.randn(M, H, generator=g).to(TORCH_DTYPE[dtype])
     w = torch.randn(H, generator=g).to(TORCH_DTYPE[dtype])
     return x, w, float(1.0 if gs is None else gs)
+
+
+def add_inputs(case):
+    dtype, M, H, block, fmt, swizzled, both, gs = case
+    g = torch.Generator().manual_seed(42)
+    x = torch.randn(M, H, generator=g).to(TORCH_DTYPE[dtype])
+    r = torch.randn(M, H, generator=g).to(TORCH_DTYPE[dtype])
+    w = torch.randn(H, generator=g).to(TORCH_DTYPE[dtype])
+    return x, r, w, float(1.0 if gs is None else gs)
+
+
+def run_add(case):
+    from flashinfer.norm import add_rmsnorm_fp4quant
+
+    dtype, M, H, block, fmt, swizzled, both, gs = case
+    x, r, w, _ = add_inputs(case)
+    gs_t = None if gs is None else torch.tensor([gs], dtype=torch.float32, device="cuda")
+    residual = r.cuda()
+    result = add_rmsnorm_fp4quant(x.cuda(), residual, w.cuda(), global_scale=gs_t, eps=1e-6, block_size=block,
+                                  scale_format=fmt, is_sf_swizzled_layout=swizzled, output_both_sf_layouts=both)
+    torch.cuda.synchronize()
+    out = {"packed": u8(result[0]), "sf": u8(result[1]).reshape(-1), "residual": bits(residual)}
+    if both:
+        out["sf_unswizzled"] = u8(result[2]).reshape(-1)
+    return out
 
 
 def run_quant(case, backend):
@@ -122,6 +157,9 @@ def record_mufu_tables(out_dir: Path) -> None:
         o.rmsnorm_fp4quant(bits(x), bits(w), case[0], gs, 1e-6, case[3], case[4], case[5], recorder)
         if case[3] == 16:
             c_oracle.rmsnorm_fp4quant(bits(x), bits(w), case[0], gs, 1e-6, case[5], recorder)
+    for case in ADD_CASES:
+        x, r, w, gs = add_inputs(case)
+        o.add_rmsnorm_fp4quant(bits(x), bits(r), bits(w), case[0], gs, 1e-6, case[3], case[4], case[5], recorder)
     np.savez_compressed(out_dir / "mufu_tables.npz", **recorder.arrays())
 
 
@@ -152,6 +190,17 @@ def main():
             packed, sf = run_rms(case)
             entry["input_sha256"] = digest(bits(x), bits(w), np.float32(gs))
             np.savez_compressed(out_dir / f"rms_{i}.npz", packed=packed, sf=sf, global_scale=np.float32(gs))
+            entry["status"] = "ok"
+        except Exception as error:
+            entry.update(status="failed", error=f"{type(error).__name__}: {error}", trace=traceback.format_exc()[-1200:])
+        manifest["cases"].append(entry)
+    for i, case in enumerate(ADD_CASES):
+        entry = {"name": f"add_{i}", "kind": "add_rmsnorm_fp4quant", "case": list(case)}
+        try:
+            x, r, w, gs = add_inputs(case)
+            out = run_add(case)
+            entry["input_sha256"] = digest(bits(x), bits(r), bits(w), np.float32(gs))
+            np.savez_compressed(out_dir / f"add_{i}.npz", global_scale=np.float32(gs), **out)
             entry["status"] = "ok"
         except Exception as error:
             entry.update(status="failed", error=f"{type(error).__name__}: {error}", trace=traceback.format_exc()[-1200:])

@@ -42,6 +42,17 @@ def make_provider(native, *, prefer_c: bool = True):
             layout = "128x4" if cfg["swizzled"] else "linear"
             logical = nvfp4_oracle.logical_scales(sf, M, cols, layout)
             return torch.from_numpy(packed), torch.from_numpy(np.ascontiguousarray(logical))
+        if kernel == "flashinfer_add_rmsnorm_fp4quant":
+            cfg = kw["config"]
+            dtype = cfg["input_dtype"]
+            out = nvfp4_oracle.add_rmsnorm_fp4quant(
+                to_bits(kw["x"]), to_bits(kw["residual"]), to_bits(kw["weight"]), dtype,
+                float(kw["global_scale"].item()), float(cfg["eps"]), int(cfg["block_size"]),
+                str(cfg["scale_format"]), False, mufu)
+            tdtype = {"float16": torch.float16, "bfloat16": torch.bfloat16}[dtype]
+            as_tensor = lambda bits: torch.from_numpy(bits.view(np.int16).copy()).view(tdtype)
+            return {"y": torch.from_numpy(out["y"]), "scale": torch.from_numpy(out["scale"]),
+                    "y_norm": as_tensor(out["y_norm"]), "residual": as_tensor(out["residual"])}
         if kernel == "nvfp4_gemm":
             return gemm_expected(kw)
         raise KeyError(kernel)

@@ -34,7 +34,7 @@ CASES = {c["name"]: c for c in MANIFEST["cases"] if c["status"] == "ok"}
 
 
 def test_manifest_is_complete():
-    assert len(CASES) == len(GEN.QUANT_CASES) + len(GEN.RMS_CASES)
+    assert len(CASES) == len(GEN.QUANT_CASES) + len(GEN.RMS_CASES) + len(GEN.ADD_CASES)
     assert MANIFEST["mufu_tables"] == "ok"
     assert all(c.get("cuda_backend_identical", True) for c in CASES.values())
 
@@ -69,6 +69,25 @@ def test_rmsnorm_oracle_matches_flashinfer_bytes(index):
         packed_c, sf_c = c_oracle.rmsnorm_fp4quant(GEN.bits(x), GEN.bits(w), dtype, gs, 1e-6, swizzled, TABLE)
         assert np.array_equal(packed_c, packed)
         assert np.array_equal(o.logical_scales(sf_c, M, H // block, layout), mine)
+
+
+@pytest.mark.parametrize("index", range(len(GEN.ADD_CASES)))
+def test_add_rmsnorm_oracle_matches_flashinfer_bytes(index):
+    case = GEN.ADD_CASES[index]
+    entry, gold = CASES[f"add_{index}"], np.load(GOLDEN / f"add_{index}.npz")
+    x, r, w, gs = GEN.add_inputs(case)
+    assert GEN.digest(GEN.bits(x), GEN.bits(r), GEN.bits(w), np.float32(gs)) == entry["input_sha256"], \
+        "seeded input drifted"
+    dtype, M, H, block, fmt, swizzled, both, _ = case
+    out = o.add_rmsnorm_fp4quant(GEN.bits(x), GEN.bits(r), GEN.bits(w), dtype, gs, 1e-6, block, fmt,
+                                 swizzled or both, TABLE)
+    assert np.array_equal(out["residual"].reshape(-1), gold["residual"].reshape(-1))
+    assert np.array_equal(out["y"].reshape(-1), gold["packed"].reshape(-1))
+    layout = "128x4" if (swizzled or both) else "linear"
+    theirs = o.logical_scales(gold["sf"], M, H // block, layout)
+    assert np.array_equal(out["scale"], theirs)
+    if both:
+        assert np.array_equal(out["scale"].reshape(-1), gold["sf_unswizzled"].reshape(-1)[: out["scale"].size])
 
 
 def test_exact_rounding_is_not_what_the_hardware_does():

@@ -59,11 +59,12 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
         _native.lib()
 
 
-def test_registry_indexes_the_three_kernels_without_importing_them():
+def test_registry_indexes_the_kernels_without_importing_them():
     from tirx_kernels import registry
 
     index = registry.kernel_index(strict=True)
-    assert sorted(index) == ["flashinfer_rmsnorm_fp4quant", "nvfp4_gemm", "nvfp4_quantize"]
+    assert sorted(index) == ["flashinfer_add_rmsnorm_fp4quant", "flashinfer_rmsnorm_fp4quant", "nvfp4_gemm",
+                             "nvfp4_quantize"]
     assert index["nvfp4_gemm"].category == "basic" and index["nvfp4_quantize"].category == "flashinfer"
     assert index["nvfp4_quantize"].module_name == "tirx_kernels.flashinfer.quantization.nvfp4_quantize"
     with pytest.raises(KeyError):
@@ -155,7 +156,7 @@ def test_registry_cli_lists_kernels():
     listing = _cli("tirx_kernels.registry", "--format", "json")
     assert listing.returncode == 0
     names = [entry["name"] for entry in json.loads(listing.stdout)]
-    assert names == ["flashinfer_rmsnorm_fp4quant", "nvfp4_gemm", "nvfp4_quantize"]
+    assert names == ["flashinfer_add_rmsnorm_fp4quant", "flashinfer_rmsnorm_fp4quant", "nvfp4_gemm", "nvfp4_quantize"]
     runs = _cli("tirx_kernels.registry", "--format", "benchrun", "--category", "basic")
     assert "nvfp4_gemm|8192x8192x8192|python -m tirx_kernels.bench --kernel nvfp4_gemm" in runs.stdout
 

@@ -34,7 +34,7 @@ COMMON_FLAGS = [
     f"-I{INCLUDE}",
 ]
 
-MAIN_SOURCES = ["capi.cu", "quantize.cu", "rmsnorm_fp4quant.cu", "nvfp4_gemm.cu"]
+MAIN_SOURCES = ["capi.cu", "quantize.cu", "rmsnorm_fp4quant.cu", "add_rmsnorm_fp4quant.cu", "nvfp4_gemm.cu"]
 CUBLASLT_SOURCES = ["cublaslt_baseline.cu"]
 
 

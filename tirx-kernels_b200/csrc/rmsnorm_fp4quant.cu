@@ -16,6 +16,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "norm_quant.cuh"
 
 namespace b2 {
 namespace {
@@ -39,20 +40,6 @@ struct RmsParams {
   float inv_h;       // 1.0f / H (exact when pow2)
   int enable_pdl;
 };
-
-// rmsnorm_fp4quant.py _cvt_f32_to_ue8m0 :155-171
-__device__ __forceinline__ uint32_t cvt_f32_to_ue8m0(float v) {
-  const bool is_zero = v <= 0.0f;
-  int r = __float2int_ru(lg2_approx(v)) + 127;
-  r = r < 0 ? 0 : r;
-  r = r > 255 ? 255 : r;
-  return is_zero ? 0u : static_cast<uint32_t>(r);
-}
-// rmsnorm_fp4quant.py _ue8m0_to_output_scale :174-185
-__device__ __forceinline__ float ue8m0_to_output_scale(uint32_t code) {
-  const float cand = ex2_approx(__int2float_rn(127 - static_cast<int>(code)));
-  return code == 0u ? 0.0f : cand;
-}
 
 // acc + x*x for eight values in element order.  The square of a bf16/fp16 value is exact in fp32,
 // so one FMA per element rounds exactly like the reference's mul.f32 followed by add.f32.
@@ -307,22 +294,6 @@ __global__ void __launch_bounds__(TPR == 256 ? 256 : 128)
 // lane + 32, ... before the final butterfly.  Same here: 256 threads per CTA, one row per cluster,
 // partials written into every CTA's shared memory through distributed shared memory, one
 // hardware cluster barrier, then the quantization pass over this CTA's own columns.
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void st_cluster_f32(const float* local, uint32_t target_cta, float v) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
-               : "=r"(remote)
-               : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(local))), "r"(target_cta));
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
-}
-__device__ __forceinline__ void cluster_barrier() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
 template <typename Tag, int BLOCK>
 __global__ void __launch_bounds__(256) rmsnorm_fp4quant_cluster_kernel(const __grid_constant__ RmsParams p, int cluster_n) {
   constexpr int kTpr = 256, kWarps = 8;
@@ -455,7 +426,6 @@ int launch_cluster(const RmsParams& p, int cluster_n, cudaStream_t stream) {
 
 // rmsnorm_fp4quant.py _derived_config / _estimate_smem / _source_config :358-400: the smallest
 // cluster size whose per-CTA row tile fits in shared memory.
-int threads_per_row(int h);
 int source_cluster_n(int H) {
   for (int cand = 1; cand <= 16; cand *= 2) {
     const int hpc = H / cand;
@@ -470,16 +440,6 @@ int source_cluster_n(int H) {
     if (H % cand == 0 && est <= 232448) return cand;
   }
   return 16;
-}
-
-// rmsnorm_fp4quant.py _threads_per_row :344-355
-int threads_per_row(int h) {
-  if (h <= 64) return 8;
-  if (h <= 128) return 16;
-  if (h <= 3072) return 32;
-  if (h <= 6144) return 64;
-  if (h <= 16384) return 128;
-  return 256;
 }
 
 template <typename Kernel>

@@ -30,6 +30,7 @@ MAIN_SIGNATURES = {
     "b2_nvfp4_quantize": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "b2_nvfp4_sf_bytes": (_i64, [_i, _i, _i]),
     "b2_rmsnorm_fp4quant": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _vp]),
+    "b2_add_rmsnorm_fp4quant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "b2_nvfp4_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "b2_nvfp4_gemm_small_m_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "b2_nvfp4_gemm_status": (_i, [_vp]),
@@ -161,6 +162,20 @@ def rmsnorm_fp4quant(x, weight, y, scales, global_scale, M: int, H: int, eps: fl
                                   SCALE_FORMAT_CODES[scale_format], int(swizzled), int(enable_pdl),
                                   current_stream_ptr()),
         "b2_rmsnorm_fp4quant",
+    )
+
+
+def add_rmsnorm_fp4quant(x, residual, weight, y, scales, scales_unswizzled, y_norm, global_scale, M: int, H: int,
+                         eps: float, dtype: str, block_size: int, scale_format: str, swizzled: bool,
+                         output_both_sf_layouts: bool, output_norm: bool, enable_pdl: bool) -> None:
+    _require_cuda(x, residual, weight, y, scales, scales_unswizzled, y_norm, global_scale)
+    check(
+        lib().b2_add_rmsnorm_fp4quant(_ptr(x), _ptr(residual), _ptr(weight), _ptr(y), _ptr(scales),
+                                      _ptr(scales_unswizzled), _ptr(y_norm), _ptr(global_scale), M, H, float(eps),
+                                      DTYPE_CODES[dtype], block_size, SCALE_FORMAT_CODES[scale_format],
+                                      int(swizzled), int(output_both_sf_layouts), int(output_norm),
+                                      int(enable_pdl), current_stream_ptr()),
+        "b2_add_rmsnorm_fp4quant",
     )
 
 
