@@ -303,6 +303,17 @@ def extras(args, rank: int, world: int, distributed: bool) -> dict:
             rms.algorithmic_bytes(8192, 7168, 16, True), us)}
         del data, output
 
+        # residual add + RMSNorm + quantize 8192 x 7168 (385 MB per launch > L2)
+        from tirx_kernels.flashinfer.norm import add_rmsnorm_fp4quant as addrms
+
+        cfg = next(c for c in addrms.BENCH_CONFIGS if c["case"] == "bench_nv_swizzled_large")
+        data, output = addrms._prepare_tensors(cfg), addrms._prepare_output(cfg)
+        exa = addrms.get_kernel(**{kk: v for kk, v in cfg.items() if kk != "label"}).config["launcher"]
+        us = _bench_us(lambda: addrms._launch(exa, data, output, cfg), reps=30)
+        out["add_rmsnorm_fp4quant_bf16_m8192_h7168_swizzled"] = {"us": us, "roofline": _checks.roofline_hbm(
+            addrms.algorithmic_bytes(8192, 7168, 16, False, False), us)}
+        del data, output
+
         # GEMM 8192^3 (205 MB touched per launch > L2) and the decode shape
         for (M, N, K) in ((8192, 8192, 8192), (16, 8192, 8192)):
             A_fp4, B_fp4, A_sf, B_sf, alpha, C_ref = gemm.prepare_data(M, N, K)
