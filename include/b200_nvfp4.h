@@ -69,6 +69,20 @@ int b2_abi_version(void);
 int b2_nvfp4_quantize(const void* in, void* out, void* sf, const float* gs_dev, int m, int k,
                       int in_dtype, int sf_layout, int fuse_silu, int enable_pdl, void* stream);
 
+/*
+ * Per-token NVFP4 quantizer: the executable of
+ * tirx_kernels/flashinfer/quantization/nvfp4_quantize_per_token.py:142-232, called as
+ * ex(a_flat, out_flat, sf, pts, m, gs_inv) in run_test :321.  Every row gets its own scale:
+ * token_scale[r] = amax(row r) * gs_inv[0] (0 for an all-zero row), and the blocks of the row are
+ * quantized with 1 / token_scale in place of the global scale.
+ *   in [m, k] fp16/bf16; out [m, k/2]; sf in `sf_layout` (b2_nvfp4_sf_bytes); token_scale [m] fp32
+ * Padding columns AND padding rows of the swizzled layouts are zero-filled by the call (the
+ * reference leaves the rows to a zero-initialised buffer from its host wrapper, :262-264).
+ */
+int b2_nvfp4_quantize_per_token(const void* in, void* out, void* sf, float* token_scale,
+                                const float* gs_inv_dev, int m, int k, int in_dtype, int sf_layout,
+                                int enable_pdl, void* stream);
+
 /* Number of bytes of the scale-factor buffer for (m, k, sf_layout); mirrors
  * _sf_numel, tirx_kernels/flashinfer/quantization/nvfp4_quantize.py:126-129. */
 int64_t b2_nvfp4_sf_bytes(int m, int k, int sf_layout);

@@ -313,6 +313,58 @@ def nvfp4_quantize(x_bits, dtype: str, global_scale, sf_layout: str = "128x4", f
     return packed, sf
 
 
+FLOAT32_MAX = np.float32(3.4028234663852886e38)
+
+
+def nvfp4_quantize_per_token(x_bits, dtype: str, gs_inv, sf_layout: str = "128x4", mufu=None):
+    """tirx_kernels/flashinfer/quantization/nvfp4_quantize_per_token.py: row scales :195-211, block
+    recipe _process_block_pt :56-74 (nvfp4_compute_output_scale, fp_quant_kern.py:377-394), SF
+    placement and column padding :216-229; padding rows are zero (host-initialised buffer, :262-264).
+
+    Returns (packed uint8 [m, k/2], sf uint8 [sf_buffer_size], token_scale float32 [m]).
+
+    PARITY UNPINNED: the reference takes its expected bytes from flashinfer's CuTe-DSL per-token
+    kernel, which the flashinfer build available here (0.6.11) does not contain; that build's CUDA
+    per-token path is a different implementation and agrees with this restatement on > 99.5 % of the
+    bytes (tests/test_golden_cpu.py bounds the distance).  The block recipe itself is the pinned
+    one of nvfp4_quantize with the row's encode scale in place of the global scale.
+    """
+    mufu = mufu or ExactMufu()
+    x_bits = np.asarray(x_bits, dtype=np.uint16)
+    m, k = x_bits.shape
+    if k <= 0 or k % 16:
+        raise ValueError(f"k={k} outside the source dispatch domain (k % 16 != 0)")
+    x = bits_to_f32(x_bits, dtype)
+    nsb = k // 16
+    blocks = x.reshape(m, nsb, 16)
+    with np.errstate(invalid="ignore"):
+        amax = np.fmax.reduce(np.abs(blocks), axis=-1).astype(np.float32)
+        row_amax = np.fmax.reduce(amax, axis=-1).astype(np.float32)
+    zero = row_amax == 0.0
+    with np.errstate(over="ignore", invalid="ignore"):
+        token = np.where(zero, np.float32(0.0), (row_amax * np.float32(gs_inv)).astype(np.float32)).astype(np.float32)
+    encode = np.where(zero, FLOAT32_MAX, mufu.rcp_ftz(np.where(zero, np.float32(1.0), token))).astype(np.float32)
+    rcp6 = mufu.rcp_ftz(np.array([6.0], dtype=np.float32))[0]
+    with np.errstate(over="ignore", invalid="ignore"):
+        scale = (encode[:, None] * (amax * rcp6).astype(np.float32)).astype(np.float32)
+    sf_code = e4m3_encode(scale)
+    sf_f32 = e4m3_decode(sf_code)
+    rcp_enc = mufu.rcp_ftz(encode)
+    with np.errstate(over="ignore", invalid="ignore"):
+        prod = (sf_f32 * rcp_enc[:, None]).astype(np.float32)
+    inv = mufu.rcp_ftz(prod)
+    out_scale = np.where(sf_f32 == 0.0, np.float32(0.0), inv).astype(np.float32)
+    with np.errstate(over="ignore", invalid="ignore"):
+        scaled = (blocks * out_scale[..., None]).astype(np.float32)
+    packed = pack_nibbles(e2m1_encode(scaled).reshape(m, k))
+    if sf_layout == "linear":
+        return packed, sf_code.reshape(-1).copy(), token
+    pad_cols = padded_sf_cols(nsb)
+    sf = np.zeros(sf_buffer_size(m, nsb, sf_layout), dtype=np.uint8)
+    sf[sf_offsets(sf_layout, np.arange(m)[:, None], np.arange(nsb)[None, :], pad_cols)] = sf_code
+    return packed, sf, token
+
+
 # --------------------------------------------------------------------------------------
 # flashinfer_rmsnorm_fp4quant  (tirx_kernels/flashinfer/norm/rmsnorm_fp4quant.py)
 # --------------------------------------------------------------------------------------

@@ -6,7 +6,8 @@ The reference's tests take their expected bytes from flashinfer at test time
 (`flashinfer.quantization.nvfp4_quantize(backend="cute-dsl")`,
 tirx_kernels/flashinfer/quantization/nvfp4_quantize.py:418-438, and
 `flashinfer.cute_dsl.rmsnorm_fp4quant`, tirx_kernels/flashinfer/norm/rmsnorm_fp4quant.py:1187-1215,
-`flashinfer.norm.add_rmsnorm_fp4quant`, tirx_kernels/flashinfer/norm/add_rmsnorm_fp4quant.py:1508-1555)
+`flashinfer.norm.add_rmsnorm_fp4quant`, tirx_kernels/flashinfer/norm/add_rmsnorm_fp4quant.py:1508-1555,
+`nvfp4_quantize(..., per_token_activation=True)`, .../quantization/nvfp4_quantize_per_token.py:278-291)
 and store none.  This script runs the flashinfer build installed in this image (0.6.11, not the
 revision the reference pins) on seeded inputs drawn on the CPU and stores its OUTPUTS as small
 .npz files (inputs are regenerated from the seed by `quant_inputs` / `rms_inputs`; their SHA-256
@@ -49,6 +50,13 @@ RMS_CASES = [
     ("bfloat16", 8, 2048, 32, "ue8m0", False, None),
     ("float16", 3, 3088, 16, "e4m3", False, 3.25),
 ]
+PER_TOKEN_CASES = [
+    # (dtype, m, k, layout, zero_row); the inverse global scale is 1 / (448 * 6)
+    ("float16", 13, 1040, "linear", False),
+    ("bfloat16", 40, 1024, "128x4", True),
+    ("float16", 13, 1024, "8x4", False),
+    ("bfloat16", 6, 8256, "128x4", False),
+]
 ADD_CASES = [
     # (dtype, M, H, block, scale_format, swizzled, both_layouts, global_scale)
     ("bfloat16", 5, 4096, 16, "e4m3", True, False, None),
@@ -90,6 +98,27 @@ def rms_inputs(case):
     x = torch.randn(M, H, generator=g).to(TORCH_DTYPE[dtype])
     w = torch.randn(H, generator=g).to(TORCH_DTYPE[dtype])
     return x, w, float(1.0 if gs is None else gs)
+
+
+def per_token_inputs(case):
+    dtype, m, k, layout, zero_row = case
+    g = torch.Generator().manual_seed(42)
+    a = torch.randn(m, k, generator=g).to(TORCH_DTYPE[dtype])
+    if zero_row:
+        a[0].zero_()
+    return a, float(np.float32(1.0 / (448.0 * 6.0)))
+
+
+def run_per_token(case):
+    from flashinfer import SfLayout
+    from flashinfer.quantization import nvfp4_quantize
+
+    a, gs_inv = per_token_inputs(case)
+    gs_t = torch.tensor([gs_inv], dtype=torch.float32, device="cuda")
+    enum = {"linear": SfLayout.layout_linear, "128x4": SfLayout.layout_128x4, "8x4": SfLayout.layout_8x4}[case[3]]
+    out, sf, pts = nvfp4_quantize(a.cuda(), gs_t, sfLayout=enum, backend="cuda", per_token_activation=True)
+    torch.cuda.synchronize()
+    return u8(out), u8(sf).reshape(-1), pts.detach().cpu().float().numpy().reshape(-1)
 
 
 def add_inputs(case):
@@ -157,6 +186,9 @@ def record_mufu_tables(out_dir: Path) -> None:
         o.rmsnorm_fp4quant(bits(x), bits(w), case[0], gs, 1e-6, case[3], case[4], case[5], recorder)
         if case[3] == 16:
             c_oracle.rmsnorm_fp4quant(bits(x), bits(w), case[0], gs, 1e-6, case[5], recorder)
+    for case in PER_TOKEN_CASES:
+        a, gs_inv = per_token_inputs(case)
+        o.nvfp4_quantize_per_token(bits(a), case[0], gs_inv, case[3], recorder)
     for case in ADD_CASES:
         x, r, w, gs = add_inputs(case)
         o.add_rmsnorm_fp4quant(bits(x), bits(r), bits(w), case[0], gs, 1e-6, case[3], case[4], case[5], recorder)
@@ -190,6 +222,18 @@ def main():
             packed, sf = run_rms(case)
             entry["input_sha256"] = digest(bits(x), bits(w), np.float32(gs))
             np.savez_compressed(out_dir / f"rms_{i}.npz", packed=packed, sf=sf, global_scale=np.float32(gs))
+            entry["status"] = "ok"
+        except Exception as error:
+            entry.update(status="failed", error=f"{type(error).__name__}: {error}", trace=traceback.format_exc()[-1200:])
+        manifest["cases"].append(entry)
+    for i, case in enumerate(PER_TOKEN_CASES):
+        entry = {"name": f"pertoken_{i}", "kind": "nvfp4_quantize_per_token", "case": list(case)}
+        try:
+            a, gs_inv = per_token_inputs(case)
+            packed, sf, pts = run_per_token(case)
+            entry["input_sha256"] = digest(bits(a), np.float32(gs_inv))
+            np.savez_compressed(out_dir / f"pertoken_{i}.npz", packed=packed, sf=sf, token_scale=pts,
+                                gs_inv=np.float32(gs_inv))
             entry["status"] = "ok"
         except Exception as error:
             entry.update(status="failed", error=f"{type(error).__name__}: {error}", trace=traceback.format_exc()[-1200:])

@@ -32,6 +32,10 @@ def make_provider(native, *, prefer_c: bool = True):
                 packed, sf = nvfp4_oracle.nvfp4_quantize(bits, kw["dtype"], gs, kw["sf_layout"],
                                                          kw["fuse_silu"], mufu)
             return torch.from_numpy(packed), torch.from_numpy(sf)
+        if kernel == "nvfp4_quantize_per_token":
+            packed, sf, pts = nvfp4_oracle.nvfp4_quantize_per_token(
+                to_bits(kw["a"]), kw["dtype"], float(kw["gs_inv"].item()), kw["sf_layout"], mufu)
+            return torch.from_numpy(packed), torch.from_numpy(sf), torch.from_numpy(pts)
         if kernel == "flashinfer_rmsnorm_fp4quant":
             cfg = kw["config"]
             packed, sf = nvfp4_oracle.rmsnorm_fp4quant(

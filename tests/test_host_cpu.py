@@ -64,7 +64,7 @@ def test_registry_indexes_the_kernels_without_importing_them():
 
     index = registry.kernel_index(strict=True)
     assert sorted(index) == ["flashinfer_add_rmsnorm_fp4quant", "flashinfer_rmsnorm_fp4quant", "nvfp4_gemm",
-                             "nvfp4_quantize"]
+                             "nvfp4_quantize", "nvfp4_quantize_per_token"]
     assert index["nvfp4_gemm"].category == "basic" and index["nvfp4_quantize"].category == "flashinfer"
     assert index["nvfp4_quantize"].module_name == "tirx_kernels.flashinfer.quantization.nvfp4_quantize"
     with pytest.raises(KeyError):
@@ -94,7 +94,8 @@ def test_registry_rejects_bad_metadata(tmp_path, monkeypatch):
 def test_config_labels_are_unique_and_keep_the_reference_vocabulary():
     from tirx_kernels import registry
 
-    for name in ("nvfp4_gemm", "nvfp4_quantize", "flashinfer_rmsnorm_fp4quant"):
+    for name in ("nvfp4_gemm", "nvfp4_quantize", "nvfp4_quantize_per_token", "flashinfer_rmsnorm_fp4quant",
+                 "flashinfer_add_rmsnorm_fp4quant"):
         module = registry.load_kernel(name)
         for configs in (module.CONFIGS, getattr(module, "BENCH_CONFIGS", [])):
             labels = [c["label"] for c in configs]
@@ -106,6 +107,8 @@ def test_config_labels_are_unique_and_keep_the_reference_vocabulary():
     assert [c["label"] for c in gemm.CONFIGS][:5] == [f"{s}x{s}x{s}" for s in (1024, 2048, 4096, 8192, 16384)]
     rms = registry.load_kernel("flashinfer_rmsnorm_fp4quant")
     assert len(rms.CONFIGS) == 1025
+    assert len(registry.load_kernel("flashinfer_add_rmsnorm_fp4quant").CONFIGS) == 1245
+    assert len(registry.load_kernel("nvfp4_quantize_per_token").CONFIGS) == 17
 
 
 def test_runner_prepared_benchmark_contract():
@@ -156,7 +159,8 @@ def test_registry_cli_lists_kernels():
     listing = _cli("tirx_kernels.registry", "--format", "json")
     assert listing.returncode == 0
     names = [entry["name"] for entry in json.loads(listing.stdout)]
-    assert names == ["flashinfer_add_rmsnorm_fp4quant", "flashinfer_rmsnorm_fp4quant", "nvfp4_gemm", "nvfp4_quantize"]
+    assert names == ["flashinfer_add_rmsnorm_fp4quant", "flashinfer_rmsnorm_fp4quant", "nvfp4_gemm", "nvfp4_quantize",
+                     "nvfp4_quantize_per_token"]
     runs = _cli("tirx_kernels.registry", "--format", "benchrun", "--category", "basic")
     assert "nvfp4_gemm|8192x8192x8192|python -m tirx_kernels.bench --kernel nvfp4_gemm" in runs.stdout
 

@@ -197,6 +197,154 @@ int dispatch_layout(const QuantParams& p, int layout, bool silu, bool v8, cudaSt
   }
 }
 
+// ---- per-token variant (tirx_kernels/flashinfer/quantization/nvfp4_quantize_per_token.py) -------
+// One CTA of 128 threads per row, as in the reference (:142-232): row maximum, token scale
+// = amax * gs_inv, encode scale = rcp(token scale) (FLT_MAX for an all-zero row, :203-211), then
+// the ordinary block recipe with the row's encode scale in place of the global scale (:56-74).
+// Unlike the reference, which reads the row twice, the blocks a thread owns (t, t + 128, ...)
+// stay in registers between the two passes when the row has at most 128 * NB blocks, and rows
+// past m (padding rows of the swizzled layouts) are zero-filled by extra CTAs instead of the host.
+struct PerTokenParams {
+  const uint8_t* in;
+  uint8_t* out;
+  uint8_t* sf;
+  float* token_scale;  // [m]
+  const float* gs_inv;
+  int m;
+  int k;
+  int nsb;
+  int pad_cols;
+  int enable_pdl;
+};
+
+template <int LAYOUT>
+__device__ __forceinline__ int64_t sf_offset_any(int row, int col, int nsb, int pad_cols) {
+  if constexpr (LAYOUT == B2_SF_LINEAR) return static_cast<int64_t>(row) * nsb + col;
+  else if constexpr (LAYOUT == B2_SF_128x4) return sf_offset_128x4(row, col, pad_cols);
+  else return sf_offset_8x4(row, col, pad_cols);
+}
+
+template <typename Tag>
+__device__ __forceinline__ float block_amax(const uint32_t (&w)[8]) {
+  const uint32_t lo4[4] = {w[0], w[1], w[2], w[3]};
+  const uint32_t hi4[4] = {w[4], w[5], w[6], w[7]};
+  return pair_max_to_f32<Tag>(hmax2<Tag>(absmax_4<Tag>(lo4), absmax_4<Tag>(hi4)));
+}
+
+template <typename Tag, int LAYOUT, bool V8, int NB>
+__global__ void __launch_bounds__(128) nvfp4_quantize_per_token_kernel(const __grid_constant__ PerTokenParams p) {
+  constexpr int kThreads = 128;
+  __shared__ float red[4];
+  const int row = blockIdx.x;
+  const int t = threadIdx.x;
+  if (p.enable_pdl) pdl_wait();
+  if (row >= p.m) {  // padding row of a swizzled layout
+    for (int c = t; c < p.pad_cols; c += kThreads) p.sf[sf_offset_any<LAYOUT>(row, c, p.nsb, p.pad_cols)] = 0;
+    return;
+  }
+  const uint8_t* in_row = p.in + static_cast<int64_t>(row) * p.k * 2;
+  uint8_t* out_row = p.out + static_cast<int64_t>(row) * (p.k >> 1);
+
+  uint32_t w[NB > 0 ? NB : 1][8];
+  float local = 0.0f;
+  if constexpr (NB > 0) {
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+      const int col = t + j * kThreads;
+      if (col < p.nsb) load_block<V8>(in_row + col * 32, w[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < NB; ++j)
+      if (t + j * kThreads < p.nsb) local = max_f32(local, block_amax<Tag>(w[j]));
+  } else {
+    for (int col = t; col < p.nsb; col += kThreads) {
+      load_block<V8>(in_row + col * 32, w[0]);
+      local = max_f32(local, block_amax<Tag>(w[0]));
+    }
+  }
+#pragma unroll
+  for (int x = 1; x < 32; x <<= 1) local = max_f32(local, __shfl_xor_sync(0xFFFFFFFFu, local, x));
+  if ((t & 31) == 0) red[t >> 5] = local;
+  __syncthreads();
+  float row_amax = (t & 31) < 4 ? red[t & 31] : 0.0f;
+#pragma unroll
+  for (int x = 1; x < 32; x <<= 1) row_amax = max_f32(row_amax, __shfl_xor_sync(0xFFFFFFFFu, row_amax, x));
+
+  const float gs_inv = *p.gs_inv;
+  float encode = 3.4028234663852886e38f, token = 0.0f;
+  if (row_amax != 0.0f) {
+    token = mul_f32(row_amax, gs_inv);
+    encode = rcp_approx_ftz(token);
+  }
+  if (t == 0) p.token_scale[row] = token;
+  const float rcp_enc = rcp_approx_ftz(encode);
+  const float rcp6 = rcp_approx_ftz(6.0f);
+
+  auto emit = [&](const uint32_t(&blk)[8], int col) {
+    uint32_t sf_byte;
+    uint2 packed;
+    quantize_block<Tag>(blk, encode, rcp_enc, rcp6, sf_byte, packed);
+    p.sf[sf_offset_any<LAYOUT>(row, col, p.nsb, p.pad_cols)] = static_cast<uint8_t>(sf_byte);
+    *reinterpret_cast<uint2*>(out_row + col * 8) = packed;
+  };
+  if constexpr (NB > 0) {
+#pragma unroll
+    for (int j = 0; j < NB; ++j)
+      if (t + j * kThreads < p.nsb) emit(w[j], t + j * kThreads);
+  } else {
+    for (int col = t; col < p.nsb; col += kThreads) {
+      load_block<V8>(in_row + col * 32, w[0]);  // second read of the row: served by L2
+      emit(w[0], col);
+    }
+  }
+  if constexpr (LAYOUT != B2_SF_LINEAR) {
+    for (int c = p.nsb + t; c < p.pad_cols; c += kThreads) p.sf[sf_offset_any<LAYOUT>(row, c, p.nsb, p.pad_cols)] = 0;
+  }
+  if (p.enable_pdl) pdl_launch_dependents();
+}
+
+template <typename Tag, int LAYOUT, bool V8>
+int launch_per_token(const PerTokenParams& p, int rows, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(rows);
+  cfg.blockDim = dim3(128);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (p.enable_pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  if (p.nsb <= 128) {
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 1>, p));
+  } else if (p.nsb <= 256) {
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 2>, p));
+  } else if (p.nsb <= 512) {
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 4>, p));
+  } else if (p.nsb <= 1024) {
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 8>, p));
+  } else {
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 0>, p));
+  }
+  return B2_OK;
+}
+
+template <typename Tag>
+int dispatch_per_token(const PerTokenParams& p, int layout, bool v8, int rows, cudaStream_t stream) {
+  switch (layout) {
+    case B2_SF_LINEAR:
+      return v8 ? launch_per_token<Tag, B2_SF_LINEAR, true>(p, rows, stream)
+                : launch_per_token<Tag, B2_SF_LINEAR, false>(p, rows, stream);
+    case B2_SF_128x4:
+      return v8 ? launch_per_token<Tag, B2_SF_128x4, true>(p, rows, stream)
+                : launch_per_token<Tag, B2_SF_128x4, false>(p, rows, stream);
+    default:
+      return v8 ? launch_per_token<Tag, B2_SF_8x4, true>(p, rows, stream)
+                : launch_per_token<Tag, B2_SF_8x4, false>(p, rows, stream);
+  }
+}
+
 }  // namespace
 }  // namespace b2
 
@@ -268,4 +416,59 @@ extern "C" int b2_nvfp4_quantize(const void* in, void* out, void* sf, const floa
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (in_dtype == B2_DTYPE_F16) return dispatch_layout<F16Tag>(p, sf_layout, fuse_silu != 0, v8, s);
   return dispatch_layout<BF16Tag>(p, sf_layout, fuse_silu != 0, v8, s);
+}
+
+extern "C" int b2_nvfp4_quantize_per_token(const void* in, void* out, void* sf, float* token_scale,
+                                           const float* gs_inv_dev, int m, int k, int in_dtype, int sf_layout,
+                                           int enable_pdl, void* stream) {
+  using namespace b2;
+  if (in_dtype != B2_DTYPE_F16 && in_dtype != B2_DTYPE_BF16) {
+    set_error("b2_nvfp4_quantize_per_token: Unsupported dtype: %d", in_dtype);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (sf_layout != B2_SF_LINEAR && sf_layout != B2_SF_128x4 && sf_layout != B2_SF_8x4) {
+    set_error("b2_nvfp4_quantize_per_token: Unsupported sf_layout: %d", sf_layout);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (m < 1) {
+    set_error("b2_nvfp4_quantize_per_token: m=%d must be >= 1", m);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (k <= 0 || k % 16 != 0) {
+    set_error("b2_nvfp4_quantize_per_token: k=%d outside the source dispatch domain (k %% 16 != 0)", k);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if (!in || !out || !sf || !token_scale || !gs_inv_dev) {
+    set_error("b2_nvfp4_quantize_per_token: null pointer argument");
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 7)) {
+    set_error("b2_nvfp4_quantize_per_token: `in` must be 16-byte and `out` 8-byte aligned");
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  PerTokenParams p;
+  p.in = static_cast<const uint8_t*>(in);
+  p.out = static_cast<uint8_t*>(out);
+  p.sf = static_cast<uint8_t*>(sf);
+  p.token_scale = token_scale;
+  p.gs_inv = gs_inv_dev;
+  p.m = m;
+  p.k = k;
+  p.nsb = k / 16;
+  p.pad_cols = p.nsb;
+  int64_t rows = m;
+  if (sf_layout != B2_SF_LINEAR) {
+    const int tile = sf_layout == B2_SF_8x4 ? 8 : 128;
+    rows = (static_cast<int64_t>(m) + tile - 1) / tile * tile;
+    p.pad_cols = (p.nsb + 3) / 4 * 4;
+  }
+  if (rows > 2147483647ll) {
+    set_error("b2_nvfp4_quantize_per_token: m=%d exceeds the grid limit", m);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  p.enable_pdl = enable_pdl ? 1 : 0;
+  const bool v8 = (reinterpret_cast<uintptr_t>(in) & 31) == 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (in_dtype == B2_DTYPE_F16) return dispatch_per_token<F16Tag>(p, sf_layout, v8, static_cast<int>(rows), s);
+  return dispatch_per_token<BF16Tag>(p, sf_layout, v8, static_cast<int>(rows), s);
 }

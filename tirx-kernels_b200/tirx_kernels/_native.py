@@ -28,6 +28,7 @@ MAIN_SIGNATURES = {
     "b2_last_error": (ctypes.c_char_p, []),
     "b2_abi_version": (_i, []),
     "b2_nvfp4_quantize": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "b2_nvfp4_quantize_per_token": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "b2_nvfp4_sf_bytes": (_i64, [_i, _i, _i]),
     "b2_rmsnorm_fp4quant": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _vp]),
     "b2_add_rmsnorm_fp4quant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _i, _i, _vp]),
@@ -150,6 +151,17 @@ def nvfp4_quantize(inp, out, sf, global_scale, m: int, k: int, dtype: str, sf_la
                                 DTYPE_CODES[dtype], SF_LAYOUT_CODES[sf_layout], int(fuse_silu),
                                 int(enable_pdl), current_stream_ptr()),
         "b2_nvfp4_quantize",
+    )
+
+
+def nvfp4_quantize_per_token(inp, out, sf, token_scale, gs_inv, m: int, k: int, dtype: str, sf_layout: str,
+                             enable_pdl: bool = False) -> None:
+    _require_cuda(inp, out, sf, token_scale, gs_inv)
+    check(
+        lib().b2_nvfp4_quantize_per_token(_ptr(inp), _ptr(out), _ptr(sf), _ptr(token_scale), _ptr(gs_inv), m, k,
+                                          DTYPE_CODES[dtype], SF_LAYOUT_CODES[sf_layout], int(enable_pdl),
+                                          current_stream_ptr()),
+        "b2_nvfp4_quantize_per_token",
     )
 
 
