@@ -1,13 +1,19 @@
-// NVFP4 block quantizer for sm_100a.
+// NVFP4 block quantizers for sm_100a.
 //
 // Arithmetic follows tirx_kernels/flashinfer/quantization/nvfp4_quantize.py:152-183
 // (_process_block) and the instruction helpers of tirx_kernels/flashinfer/utils/fp_quant.py;
-// the launch geometry does not.  The input is treated as one flat array of 32-byte
-// blocks: consecutive threads own consecutive 16-element blocks, each fetched with a
-// single 256-bit streaming load, so every warp-level request covers 1 KiB of
-// contiguous memory.  Several loads are issued per thread before the first one is
-// consumed to keep enough bytes in flight to saturate HBM3e.
+// the launch geometry does not.  Two kernels:
+//   * flat slot kernel: the input is one flat array of 32-byte blocks, consecutive threads own
+//     consecutive 16-element blocks, each fetched with a single 256-bit streaming load, several
+//     loads issued per thread before the first is consumed.  Any shape, SiLU fusion, zero fill of
+//     padding slots.
+//   * row kernel: one CTA of 128 threads per row, thread t holds blocks t, t + 128, ... of the
+//     row in registers.  It is the per-token quantizer (row maximum between load and quantize)
+//     and, without that step, the faster plain quantizer for tall activations (m >= 1024, rows of
+//     128..1024 blocks): 16384 CTAs of 48 registers keep more bytes in flight per SM than the
+//     persistent flat grid and reach the measured copy bandwidth.
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -231,7 +237,10 @@ __device__ __forceinline__ float block_amax(const uint32_t (&w)[8]) {
   return pair_max_to_f32<Tag>(hmax2<Tag>(absmax_4<Tag>(lo4), absmax_4<Tag>(hi4)));
 }
 
-template <typename Tag, int LAYOUT, bool V8, int NB>
+// PER_TOKEN = false turns the same one-CTA-per-row structure into the plain quantizer (one global
+// scale read from `gs_inv`, no row maximum, no token scales): for tall activations it keeps more
+// bytes in flight per SM than the flat slot kernel above.
+template <typename Tag, int LAYOUT, bool V8, int NB, bool PER_TOKEN = true>
 __global__ void __launch_bounds__(128) nvfp4_quantize_per_token_kernel(const __grid_constant__ PerTokenParams p) {
   constexpr int kThreads = 128;
   __shared__ float red[4];
@@ -253,30 +262,37 @@ __global__ void __launch_bounds__(128) nvfp4_quantize_per_token_kernel(const __g
       const int col = t + j * kThreads;
       if (col < p.nsb) load_block<V8>(in_row + col * 32, w[j]);
     }
+    if constexpr (PER_TOKEN) {
 #pragma unroll
-    for (int j = 0; j < NB; ++j)
-      if (t + j * kThreads < p.nsb) local = max_f32(local, block_amax<Tag>(w[j]));
-  } else {
+      for (int j = 0; j < NB; ++j)
+        if (t + j * kThreads < p.nsb) local = max_f32(local, block_amax<Tag>(w[j]));
+    }
+  } else if constexpr (PER_TOKEN) {
     for (int col = t; col < p.nsb; col += kThreads) {
       load_block<V8>(in_row + col * 32, w[0]);
       local = max_f32(local, block_amax<Tag>(w[0]));
     }
   }
+  float encode;
+  if constexpr (PER_TOKEN) {
 #pragma unroll
-  for (int x = 1; x < 32; x <<= 1) local = max_f32(local, __shfl_xor_sync(0xFFFFFFFFu, local, x));
-  if ((t & 31) == 0) red[t >> 5] = local;
-  __syncthreads();
-  float row_amax = (t & 31) < 4 ? red[t & 31] : 0.0f;
+    for (int x = 1; x < 32; x <<= 1) local = max_f32(local, __shfl_xor_sync(0xFFFFFFFFu, local, x));
+    if ((t & 31) == 0) red[t >> 5] = local;
+    __syncthreads();
+    float row_amax = (t & 31) < 4 ? red[t & 31] : 0.0f;
 #pragma unroll
-  for (int x = 1; x < 32; x <<= 1) row_amax = max_f32(row_amax, __shfl_xor_sync(0xFFFFFFFFu, row_amax, x));
-
-  const float gs_inv = *p.gs_inv;
-  float encode = 3.4028234663852886e38f, token = 0.0f;
-  if (row_amax != 0.0f) {
-    token = mul_f32(row_amax, gs_inv);
-    encode = rcp_approx_ftz(token);
+    for (int x = 1; x < 32; x <<= 1) row_amax = max_f32(row_amax, __shfl_xor_sync(0xFFFFFFFFu, row_amax, x));
+    const float gs_inv = *p.gs_inv;
+    float token = 0.0f;
+    encode = 3.4028234663852886e38f;
+    if (row_amax != 0.0f) {
+      token = mul_f32(row_amax, gs_inv);
+      encode = rcp_approx_ftz(token);
+    }
+    if (t == 0) p.token_scale[row] = token;
+  } else {
+    encode = *p.gs_inv;  // the plain quantizer's global scale
   }
-  if (t == 0) p.token_scale[row] = token;
   const float rcp_enc = rcp_approx_ftz(encode);
   const float rcp6 = rcp_approx_ftz(6.0f);
 
@@ -330,6 +346,44 @@ int launch_per_token(const PerTokenParams& p, int rows, cudaStream_t stream) {
   return B2_OK;
 }
 
+// Plain quantizer through the row kernel (register-resident sizes only).
+template <typename Tag, int LAYOUT, bool V8>
+int launch_rows(const PerTokenParams& p, int rows, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(rows);
+  cfg.blockDim = dim3(128);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (p.enable_pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  if (p.nsb <= 128) {
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 1, false>, p));
+  } else if (p.nsb <= 256) {
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 2, false>, p));
+  } else if (p.nsb <= 512) {
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 4, false>, p));
+  } else {
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 8, false>, p));
+  }
+  return B2_OK;
+}
+
+template <typename Tag>
+int dispatch_rows(const PerTokenParams& p, int layout, bool v8, int rows, cudaStream_t stream) {
+  switch (layout) {
+    case B2_SF_LINEAR:
+      return v8 ? launch_rows<Tag, B2_SF_LINEAR, true>(p, rows, stream) : launch_rows<Tag, B2_SF_LINEAR, false>(p, rows, stream);
+    case B2_SF_128x4:
+      return v8 ? launch_rows<Tag, B2_SF_128x4, true>(p, rows, stream) : launch_rows<Tag, B2_SF_128x4, false>(p, rows, stream);
+    default:
+      return v8 ? launch_rows<Tag, B2_SF_8x4, true>(p, rows, stream) : launch_rows<Tag, B2_SF_8x4, false>(p, rows, stream);
+  }
+}
+
 template <typename Tag>
 int dispatch_per_token(const PerTokenParams& p, int layout, bool v8, int rows, cudaStream_t stream) {
   switch (layout) {
@@ -344,6 +398,13 @@ int dispatch_per_token(const PerTokenParams& p, int layout, bool v8, int rows, c
                 : launch_per_token<Tag, B2_SF_8x4, false>(p, rows, stream);
   }
 }
+
+// 0: flat slot kernel always; 1: row kernel for tall activations (default); 2: row kernel whenever
+// the row fits in registers.  Read once from B2_QUANT_ROW_KERNEL (a tuning and test knob).
+int g_row_kernel_mode = [] {
+  const char* v = getenv("B2_QUANT_ROW_KERNEL");
+  return v ? atoi(v) : 1;
+}();
 
 }  // namespace
 }  // namespace b2
@@ -414,6 +475,23 @@ extern "C" int b2_nvfp4_quantize(const void* in, void* out, void* sf, const floa
   p.div_magic = (1ULL << p.div_shift) / static_cast<uint64_t>(p.slot_cols) + 1;
   const bool v8 = (reinterpret_cast<uintptr_t>(in) & 31) == 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!fuse_silu && g_row_kernel_mode != 0 && p.nsb <= 1024 &&
+      (g_row_kernel_mode == 2 || (m >= 1024 && p.nsb >= 128))) {
+    // tall activation: one CTA per row, blocks held in registers
+    PerTokenParams r;
+    r.in = p.in;
+    r.out = p.out;
+    r.sf = p.sf;
+    r.token_scale = nullptr;
+    r.gs_inv = gs_dev;
+    r.m = m;
+    r.k = k;
+    r.nsb = p.nsb;
+    r.pad_cols = p.slot_cols;
+    r.enable_pdl = p.enable_pdl;
+    if (in_dtype == B2_DTYPE_F16) return dispatch_rows<F16Tag>(r, sf_layout, v8, static_cast<int>(slot_rows), s);
+    return dispatch_rows<BF16Tag>(r, sf_layout, v8, static_cast<int>(slot_rows), s);
+  }
   if (in_dtype == B2_DTYPE_F16) return dispatch_layout<F16Tag>(p, sf_layout, fuse_silu != 0, v8, s);
   return dispatch_layout<BF16Tag>(p, sf_layout, fuse_silu != 0, v8, s);
 }
