@@ -14,6 +14,7 @@
 // (bit-identical here, the squares being exact in fp32) and the scaling multiplies
 // use the two-wide mul.f32x2.
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "norm_quant.cuh"
@@ -287,6 +288,144 @@ __global__ void __launch_bounds__(TPR == 256 ? 256 : 128)
   if (p.enable_pdl) pdl_launch_dependents();
 }
 
+// Block-owner variant of the register-resident kernel: one physical thread plays V = BLOCK / 8
+// adjacent virtual threads (v = V*q + i), so the chunks it owns for a given b, V*q + i + b*TPR, are
+// the V consecutive chunks of ONE scale block.  It keeps V running sums, combines them as the
+// first log2(V) butterfly steps would (lane l and l^1 both end up with s_l + s_(l^1)), and continues
+// the butterfly over the remaining lane bits with shuffles among the 32 / V physical lanes that
+// stand for one virtual warp.  The quantization pass then needs no shuffle at all: every thread
+// scales and packs whole blocks (one 256-bit load, one 64-bit store, one scale byte each).
+// Requires H / 8 == vb * TPR, V * vb <= 16, TPR >= 32.
+template <typename Tag, int TPR, int BLOCK, int VBMAX>
+__global__ void __launch_bounds__(128) rmsnorm_fp4quant_block_kernel(const __grid_constant__ RmsParams p) {
+  constexpr int V = BLOCK / 8;
+  constexpr int kThreads = 128;
+  constexpr int P = TPR / V;                   // physical threads per row
+  constexpr int kRows = kThreads / P;          // rows per CTA
+  constexpr int kVWarpsPerRow = TPR / 32;      // virtual warps per row
+  constexpr int kLanesPerVWarp = 32 / V;       // physical lanes standing for one virtual warp
+  __shared__ float red[kRows * kVWarpsPerRow];
+
+  const int tid = threadIdx.x;
+  const int row_in_cta = tid / P;
+  const int q = tid % P;
+  const int row = blockIdx.x * kRows + row_in_cta;
+  const bool row_valid = row < p.M;
+  const int lane = tid & 31;
+
+  if (p.enable_pdl) pdl_wait();
+  const float rcp6 = rcp_approx_ftz(6.0f);
+  const uint8_t* xrow = p.x + static_cast<int64_t>(row) * p.H * 2;
+  uint32_t c[VBMAX][V * 4];  // block b of this thread: chunks V*q + i + b*TPR, i < V
+#pragma unroll
+  for (int b = 0; b < VBMAX; ++b) {
+    if (row_valid && b < p.vb) {
+      const uint8_t* src = xrow + static_cast<int64_t>(V * q + b * TPR) * 16;
+      if constexpr (V == 2) {
+        uint32_t r[8];
+        ld_stream_256(src, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) c[b][i] = r[i];
+      } else {
+        uint32_t r0[8], r1[8];
+        ld_stream_256(src, r0);
+        ld_stream_256(src + 32, r1);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          c[b][i] = r0[i];
+          c[b][8 + i] = r1[i];
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < V * 4; ++i) c[b][i] = 0u;
+    }
+  }
+  float acc[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) acc[i] = 0.0f;
+#pragma unroll
+  for (int b = 0; b < VBMAX; ++b) {
+    if (b < p.vb) {
+#pragma unroll
+      for (int i = 0; i < V; ++i)
+        acc[i] = sum_sq_8<Tag>(acc[i], make_uint4(c[b][4 * i], c[b][4 * i + 1], c[b][4 * i + 2], c[b][4 * i + 3]));
+    }
+  }
+  float sum = add_f32(acc[0], acc[1]);
+  if constexpr (V == 4) sum = add_f32(sum, add_f32(acc[2], acc[3]));
+#pragma unroll
+  for (int x = 1; x < kLanesPerVWarp; x <<= 1) sum = add_f32(sum, __shfl_xor_sync(0xFFFFFFFFu, sum, x));
+  if constexpr (kVWarpsPerRow > 1) {
+    // virtual warp w of the row = physical lanes [w * kLanesPerVWarp, ...) of the row's threads
+    const int vwarp = q / kLanesPerVWarp;
+    if (q % kLanesPerVWarp == 0) red[row_in_cta * kVWarpsPerRow + vwarp] = sum;
+    __syncthreads();
+    float part = lane < kVWarpsPerRow ? red[row_in_cta * kVWarpsPerRow + lane] : 0.0f;
+    if constexpr (P < 32) {
+      // several rows share this physical warp: every lane reads its own row's partials
+      part = (lane % P) < kVWarpsPerRow ? red[row_in_cta * kVWarpsPerRow + (lane % P)] : 0.0f;
+    }
+#pragma unroll
+    for (int x = 1; x < 32; x <<= 1) {
+      if (P >= 32 || x < P) part = add_f32(part, __shfl_xor_sync(0xFFFFFFFFu, part, x));
+      else part = add_f32(part, 0.0f);  // lanes past the row's partials hold zero in the reference
+    }
+    sum = part;
+  }
+  const float shifted =
+      p.pow2 ? __fmaf_rn(sum, p.inv_h, p.eps) : add_f32(__fdiv_rn(sum, static_cast<float>(p.H)), p.eps);
+  const float rstd = rsqrt_approx_ftz(shifted);
+  const float gs = p.use_e4m3 ? *p.gs : 0.0f;
+  if (!row_valid) return;
+
+  const uint8_t* wbase = p.w;
+  uint8_t* yrow = p.y + static_cast<int64_t>(row) * (p.H >> 1);
+  const int64_t sf_row = p.swizzled ? sf_offset_128x4(row, 0, p.sf_pad_cols) : static_cast<int64_t>(row) * p.sf_cols;
+  uint8_t* sf_base = p.sf + sf_row;
+#pragma unroll
+  for (int b = 0; b < VBMAX; ++b) {
+    if (b < p.vb) {
+      const int j = q + b * P;  // scale block index in the row
+      uint32_t prod[V][4];
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const uint4 wc = __ldg(reinterpret_cast<const uint4*>(wbase) + j * V + i);
+        prod[i][0] = hmul2<Tag>(c[b][4 * i], wc.x);
+        prod[i][1] = hmul2<Tag>(c[b][4 * i + 1], wc.y);
+        prod[i][2] = hmul2<Tag>(c[b][4 * i + 2], wc.z);
+        prod[i][3] = hmul2<Tag>(c[b][4 * i + 3], wc.w);
+      }
+      uint32_t m2 = absmax_4<Tag>(prod[0]);
+#pragma unroll
+      for (int i = 1; i < V; ++i) m2 = hmax2<Tag>(m2, absmax_4<Tag>(prod[i]));
+      const float max_abs = mul_f32(pair_max_to_f32<Tag>(m2), rstd);
+      uint32_t code;
+      float out_scale;
+      if (p.use_e4m3) {
+        const float sc = min_f32(mul_f32(mul_f32(gs, max_abs), rcp6), 448.0f);
+        code = cvt_f32_to_e4m3(sc) & 0xFFu;
+        const float d = e4m3_to_f32(code);
+        const float r = rcp_approx_ftz(d);
+        out_scale = mul_f32(d == 0.0f ? 0.0f : r, gs);
+      } else {
+        code = cvt_f32_to_ue8m0(mul_f32(max_abs, rcp6));
+        out_scale = ue8m0_to_output_scale(code);
+      }
+      uint32_t qv[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) qv[i] = quantize_8<Tag>(prod[i], rstd, out_scale);
+      if constexpr (V == 2) {
+        *reinterpret_cast<uint2*>(yrow + j * 8) = make_uint2(qv[0], qv[1]);
+      } else {
+        *reinterpret_cast<uint4*>(yrow + j * 16) = make_uint4(qv[0], qv[1], qv[2], qv[3]);
+      }
+      sf_base[p.swizzled ? ((j >> 2) * 512 + (j & 3)) : j] = static_cast<uint8_t>(code);
+    }
+  }
+  if (p.enable_pdl) pdl_launch_dependents();
+}
+
 // ---- rows spread over a thread-block cluster (rmsnorm_fp4quant.py kernel_body :857-891) ----------
 // When one CTA cannot hold a row, the reference gives CTA c of a cluster the columns
 // [c * cols, (c + 1) * cols), lets every warp of every CTA publish its partial sum at index
@@ -442,6 +581,12 @@ int source_cluster_n(int H) {
   return 16;
 }
 
+// Tuning and test knob: B2_RMSNORM_BLOCK_OWNER=0 falls back to the per-chunk register kernel.
+int g_block_owner = [] {
+  const char* v = getenv("B2_RMSNORM_BLOCK_OWNER");
+  return v ? atoi(v) : 1;
+}();
+
 template <typename Kernel>
 int launch_config(Kernel kernel, const RmsParams& p, int rows_per_cta, int threads, size_t smem, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
@@ -466,6 +611,13 @@ int launch(const RmsParams& p, cudaStream_t stream) {
   constexpr int kRows = kThreads / TPR;
   constexpr int kWarpsPerRow = TPR >= 32 ? TPR / 32 : 1;
   if constexpr (TPR >= 32) {
+    constexpr int kV = BLOCK / 8;
+    constexpr int kBlockVb = 16 / kV;  // blocks a thread of the block-owner kernel can hold
+    if (g_block_owner && (p.H >> 3) == p.vb * TPR && p.vb <= kBlockVb &&
+        (reinterpret_cast<uintptr_t>(p.x) & 31) == 0 && (p.H % 16) == 0) {
+      constexpr int kP = TPR / kV;
+      return launch_config(rmsnorm_fp4quant_block_kernel<Tag, TPR, BLOCK, kBlockVb>, p, 128 / kP, 128, 0, stream);
+    }
     if ((p.H >> 3) == p.vb * TPR && p.vb <= 16) {
       if (p.vb <= 8) return launch_config(rmsnorm_fp4quant_reg_kernel<Tag, TPR, BLOCK, 8>, p, kRows, kThreads, 0, stream);
       return launch_config(rmsnorm_fp4quant_reg_kernel<Tag, TPR, BLOCK, 16>, p, kRows, kThreads, 0, stream);
