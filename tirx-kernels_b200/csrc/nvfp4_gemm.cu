@@ -208,6 +208,14 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
   else
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// CTA pair: one commit that arrives on the barrier at the same shared-memory offset in both
+// CTAs of the pair (a completion signal, not a load).
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(static_cast<uint16_t>(3))
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -472,14 +480,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_mma<CG>(tmem_base, a_desc + 2 * kb, b_desc + 2 * kb, kIdesc, sf_tmem + kb * 4,
                        sf_tmem + 16 + kb * 4 * L::kChunks, (ks | kb) ? 1u : 0u);
           }
-          tc_commit<CG>(empty_bar(stage));
-          if constexpr (CG == 2) tc_commit<CG>(mapa_shared(empty_bar(stage), 1));
+          if constexpr (CG == 2) tc_commit_pair(empty_bar(stage));
+          else tc_commit<CG>(empty_bar(stage));
           if (prof) t_issue += clock64() - w1;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!alive) break;
-        tc_commit<CG>(tmem_full_bar);
-        if constexpr (CG == 2) tc_commit<CG>(mapa_shared(tmem_full_bar, 1));
+        if constexpr (CG == 2) tc_commit_pair(tmem_full_bar);
+        else tc_commit<CG>(tmem_full_bar);
         acc_phase ^= 1u;
       }
       if (prof) {
