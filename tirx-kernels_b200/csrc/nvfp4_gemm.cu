@@ -271,7 +271,7 @@ struct SmemLayout {
   static_assert(kStageBytes % 1024 == 0, "stages and staging stay 1024-byte aligned");
   static_assert(kTotal <= 227 * 1024, "shared memory budget");
   static_assert(BN + STAGES * kSfCols <= 512, "tensor memory budget");
-  static_assert((4 * STAGES + 2) * 8 + 16 <= kBarrierBytes, "barrier area");
+  static_assert((3 * STAGES + 2) * 8 + 16 <= kBarrierBytes, "barrier area");
 };
 
 struct WaitCtx {
@@ -365,16 +365,16 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t bar_base = smem_base + L::kRingBytes;
-  // full: A and B of a stage landed (CTA pair: counted on the leader for both CTAs);
-  // sfload: this CTA's scale blocks landed; sfready: scales are in tensor memory (on the leader,
-  // one arrive per scale warp of the group); empty: the stage's MMAs retired.
+  // full (on the leader): A and B of a stage landed in both CTAs of the group AND every scale warp
+  // of the group has put the slab's scales into tensor memory (transaction bytes + one arrive per
+  // scale warp); sfload: this CTA's scale blocks landed in shared memory; empty: the stage's MMAs
+  // retired.
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto sfload_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  auto sfready_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (3 * STAGES + s); };
-  const uint32_t tmem_full_bar = bar_base + 8u * (4 * STAGES);
-  const uint32_t tmem_empty_bar = bar_base + 8u * (4 * STAGES + 1);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + L::kRingBytes + 8 * (4 * STAGES + 2));
+  auto empty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  const uint32_t tmem_full_bar = bar_base + 8u * (3 * STAGES);
+  const uint32_t tmem_empty_bar = bar_base + 8u * (3 * STAGES + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + L::kRingBytes + 8 * (3 * STAGES + 2));
   volatile uint32_t* abort_flag = tmem_slot + 1;
   const WaitCtx ctx{p.status, abort_flag};
 
@@ -391,9 +391,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), 1 + 4 * CG);  // the producer's expect_tx arrive + one arrive per scale warp of the group
       mbar_init(sfload_bar(s), 1);
-      mbar_init(sfready_bar(s), 4 * CG);
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(tmem_full_bar, 1);
@@ -465,8 +464,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_after();
         for (int ks = 0; ks < k_slabs; ++ks) {
           const long long w0 = prof ? clock64() : 0;
-          if (!wait_or_abort<CG == 2>(sfready_bar(stage), phase, ctx, 6u)) { alive = false; break; }
-          if (!wait_or_abort(full_bar(stage), phase, ctx, 3u)) { alive = false; break; }
+          if (!wait_or_abort<CG == 2>(full_bar(stage), phase, ctx, 3u)) { alive = false; break; }
           const long long w1 = prof ? clock64() : 0;
           t_full += w1 - w0;
           tc_fence_after();
@@ -538,8 +536,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        if (leader) mbar_arrive_local(sfready_bar(stage));
-        else mbar_arrive_cluster_relaxed(mapa_shared(sfready_bar(stage), 0));
+        if (leader) mbar_arrive_local(full_bar(stage));
+        else mbar_arrive_cluster_relaxed(mapa_shared(full_bar(stage), 0));
       }
       if (sprof) { t_wait += w1 - w0; t_body += clock64() - w1; }
     }
@@ -1088,10 +1086,10 @@ extern "C" int b2_nvfp4_gemm_status(void* stream) {
   static const char* const kWhat[] = {"",
                                       "producer waiting for a free stage",
                                       "MMA waiting for a drained accumulator",
-                                      "MMA waiting for loaded operands",
+                                      "MMA waiting for loaded operands and scale factors in tensor memory",
                                       "epilogue waiting for the accumulator",
                                       "scale warp waiting for loaded scale factors",
-                                      "MMA waiting for scale factors in tensor memory"};
+                                      "(unused)"};
   set_error("b2_nvfp4_gemm: bounded wait expired (%s) in CTA %u", host[0] < 7 ? kWhat[host[0]] : "unknown",
             host[1]);
   return B2_ERR_DEVICE_TIMEOUT;
