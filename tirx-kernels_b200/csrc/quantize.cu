@@ -241,7 +241,7 @@ __device__ __forceinline__ float block_amax(const uint32_t (&w)[8]) {
 // scale read from `gs_inv`, no row maximum, no token scales): for tall activations it keeps more
 // bytes in flight per SM than the flat slot kernel above.
 template <typename Tag, int LAYOUT, bool V8, int NB, bool PER_TOKEN = true>
-__global__ void __launch_bounds__(128) nvfp4_quantize_per_token_kernel(const __grid_constant__ PerTokenParams p) {
+__global__ void __launch_bounds__(128) nvfp4_quantize_row_kernel(const __grid_constant__ PerTokenParams p) {
   constexpr int kThreads = 128;
   __shared__ float red[4];
   const int row = blockIdx.x;
@@ -333,15 +333,15 @@ int launch_per_token(const PerTokenParams& p, int rows, cudaStream_t stream) {
     cfg.numAttrs = 1;
   }
   if (p.nsb <= 128) {
-    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 1>, p));
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_row_kernel<Tag, LAYOUT, V8, 1>, p));
   } else if (p.nsb <= 256) {
-    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 2>, p));
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_row_kernel<Tag, LAYOUT, V8, 2>, p));
   } else if (p.nsb <= 512) {
-    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 4>, p));
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_row_kernel<Tag, LAYOUT, V8, 4>, p));
   } else if (p.nsb <= 1024) {
-    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 8>, p));
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_row_kernel<Tag, LAYOUT, V8, 8>, p));
   } else {
-    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 0>, p));
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_row_kernel<Tag, LAYOUT, V8, 0>, p));
   }
   return B2_OK;
 }
@@ -361,13 +361,13 @@ int launch_rows(const PerTokenParams& p, int rows, cudaStream_t stream) {
     cfg.numAttrs = 1;
   }
   if (p.nsb <= 128) {
-    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 1, false>, p));
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_row_kernel<Tag, LAYOUT, V8, 1, false>, p));
   } else if (p.nsb <= 256) {
-    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 2, false>, p));
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_row_kernel<Tag, LAYOUT, V8, 2, false>, p));
   } else if (p.nsb <= 512) {
-    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 4, false>, p));
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_row_kernel<Tag, LAYOUT, V8, 4, false>, p));
   } else {
-    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_per_token_kernel<Tag, LAYOUT, V8, 8, false>, p));
+    B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, nvfp4_quantize_row_kernel<Tag, LAYOUT, V8, 8, false>, p));
   }
   return B2_OK;
 }
