@@ -166,7 +166,7 @@ def _chain_ms(fn, n: int, flush) -> float:
     start.record()
     for _ in range(n):
         if flush is not None:
-            flush.zero_()
+            flush.sum()  # a READ of a buffer larger than L2: evicts without leaving dirty lines behind
         if fn is not None:
             fn()
     end.record()
@@ -178,8 +178,9 @@ def _time_one(fn: Callable[[], Any], warmup_ms: float, repeat_ms: float, flush) 
     """Mean device time of one launch of `fn` in microseconds.
 
     Launches are timed back to back inside one pair of CUDA events, so the cost of the events
-    themselves is amortised.  With `flush`, every launch is preceded by a write of a buffer
-    larger than L2 (cold cache), and the time of the flush alone - measured the same way - is
+    themselves is amortised.  With `flush`, every launch is preceded by a read of a buffer
+    larger than L2 (cold cache; a write would leave 126 MB of dirty lines whose write-back the
+    timed kernel then pays for), and the time of the flush alone - measured the same way - is
     subtracted.
     """
     import torch
@@ -227,7 +228,7 @@ def bench(funcs: Mapping[str, Callable[[], Any]], *, references: Mapping[str, Ca
                 errors[name] = f"{type(error).__name__}: {error}"
     flush = None
     if timer == "event":
-        flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
+        flush = torch.zeros(L2_FLUSH_BYTES // 8, dtype=torch.int64, device="cuda")
     samples: dict[str, list[float]] = {name: [] for name in launches}
     for _ in range(rounds):
         for name, fn in launches.items():
