@@ -261,6 +261,34 @@ def _bench_us(fn, reps: int = 30, warm: int = 5) -> float:
     return start.elapsed_time(end) / reps * 1e3
 
 
+def _graph_us(launches, replays: int = 20) -> float:
+    """Device microseconds per launch of a CUDA graph holding `launches` (callables issued in order
+    on the capturing stream): removes the host's per-launch cost from small-kernel timings."""
+    import torch
+
+    for fn in launches:  # warm up outside capture: first calls configure kernels and allocate scratch
+        fn()
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        for fn in launches:
+            fn()
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            for fn in launches:
+                fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(replays):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / (replays * len(launches)) * 1e3
+
+
 def extras(args, rank: int, world: int, distributed: bool) -> dict:
     """Per-kernel numbers at the stated shapes.  Working sets exceed L2 or rotate over several buffer
     sets so that launches do not hit a warm cache."""
@@ -290,8 +318,12 @@ def extras(args, rank: int, world: int, distributed: bool) -> dict:
             quant._run_launch(ex1, xi, gs1, oi, si, m, k, "linear")
 
         us = _bench_us(q1, reps=40)
-        out["quantize_bf16_linear_m4096_k7168"] = {"us": us, "roofline": _checks.roofline_hbm(
-            quant.algorithmic_bytes(m, k, "linear"), us)}
+        state["i"] = 0
+        us_graph = _graph_us([q1] * 8)  # 8 launches over the 4 rotating sets, replayed 20 times
+        out["quantize_bf16_linear_m4096_k7168"] = {"us": us_graph, "us_with_host_launch_cost": us,
+                                                   "timing": "CUDA graph of 8 launches rotating over 4 buffer sets",
+                                                   "roofline": _checks.roofline_hbm(
+                                                       quant.algorithmic_bytes(m, k, "linear"), us_graph)}
         del sets
 
         # RMSNorm + quantize 8192 x 7168 (150 MB per launch > L2)
@@ -321,9 +353,20 @@ def extras(args, rank: int, world: int, distributed: bool) -> dict:
             D = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
             del C_ref
             exg = gemm._compile_executable(M, N, K)
-            us = _bench_us(lambda: exg(A_fp4, B_fp4, A_sf, B_sf, alpha_t, D), reps=20 if M > 16 else 100)
+            if M > 16:
+                us = _bench_us(lambda: exg(A_fp4, B_fp4, A_sf, B_sf, alpha_t, D), reps=20)
+                entry = {"us": us, "tflops": gemm.flops(M, N, K) / us / 1e6}
+            else:
+                # decode: weights (36 MB) fit in L2, so rotate over five copies (180 MB) inside a CUDA graph
+                copies = [(B_fp4.clone(), B_sf.clone()) for _ in range(5)]
+                launches = [(lambda b=b, sfb=sfb: exg(A_fp4, b, A_sf, sfb, alpha_t, D)) for b, sfb in copies] * 2
+                us = _graph_us(launches)
+                us_warm = _bench_us(lambda: exg(A_fp4, B_fp4, A_sf, B_sf, alpha_t, D), reps=100)
+                entry = {"us": us, "us_l2_warm_with_host_launch_cost": us_warm,
+                         "timing": "CUDA graph of 10 launches rotating over 5 weight copies (cold weights)",
+                         "tflops": gemm.flops(M, N, K) / us / 1e6}
+                del copies, launches
             _native.nvfp4_gemm_status()
-            entry = {"us": us, "tflops": gemm.flops(M, N, K) / us / 1e6}
             entry["roofline"] = (_checks.roofline_nvfp4(gemm.flops(M, N, K), us) if M > 16
                                  else _checks.roofline_hbm(gemm.algorithmic_bytes(M, N, K), us))
             if M > 16 and not args.no_cublaslt:
