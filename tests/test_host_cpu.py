@@ -190,3 +190,57 @@ def test_shard_bounds_and_assembly():
     full = torch.arange(6 * 8).reshape(6, 8)
     gathered = torch.stack([full[:, 0:4], full[:, 4:8]])
     assert torch.equal(ffn_tp.assemble(gathered), full)
+
+
+def test_bench_suite_workload_files_name_real_configs():
+    """Every label a workload file lists resolves to exactly one benchmark config of its kernel."""
+    import yaml
+
+    from tirx_kernels import registry
+    from tirx_kernels.bench.__main__ import find_bench_config
+
+    files = sorted((REPO / "tirx-kernels_b200" / "tirx_kernels" / "bench_suite" / "config").rglob("*.yaml"))
+    assert len(files) == 5
+    for path in files:
+        workload = yaml.safe_load(path.read_text())
+        module = registry.load_kernel(workload["kernel"])
+        assert path.stem == workload["kernel"] and workload["selection_rationale"]
+        defaults = [c for c in workload["configs"] if c["default"]]
+        assert {c["selection_role"] for c in defaults} >= {"small", "large"}
+        for entry in workload["configs"]:
+            assert find_bench_config(module, entry["config"])["label"] == entry["config"]
+
+
+def _prepared_child(*extra):
+    import socket
+
+    parent, child = socket.socketpair()
+    proc = subprocess.Popen([sys.executable, "-m", "tirx_kernels.bench", "--prepared-control-fd", str(child.fileno()),
+                             *extra], pass_fds=[child.fileno()], env={**ENV, "PATH": "/usr/bin:/bin"})
+    child.close()
+    return proc, parent, parent.makefile("r", encoding="utf-8")
+
+
+def test_prepared_child_reports_ready_without_touching_cuda_and_obeys_cancel():
+    proc, parent, reader = _prepared_child("--kernel", "nvfp4_gemm", "--config", "1024x1024x1024")
+    ready = json.loads(reader.readline())
+    assert ready["type"] == "READY" and ready["required_num_gpus"] == 1
+    assert ready["child_started"] <= ready["framework_loaded"] <= ready["module_loaded"] <= ready["ready"]
+    parent.sendall(b'{"type":"CANCEL"}\n')
+    assert proc.wait(timeout=60) == 0
+
+
+def test_prepared_child_fails_in_the_prepare_phase_for_an_unknown_config():
+    proc, parent, reader = _prepared_child("--kernel", "nvfp4_gemm", "--config", "no_such_label")
+    message = json.loads(reader.readline())
+    assert message["type"] == "FAIL" and message["phase"] == "prepare" and "no_such_label" in message["error"]
+    assert proc.wait(timeout=60) == 1
+
+
+def test_prepared_child_rejects_a_malformed_assignment():
+    proc, parent, reader = _prepared_child("--kernel", "nvfp4_quantize", "--config", "fp16_128x4_m128_k1024")
+    assert json.loads(reader.readline())["type"] == "READY"
+    parent.sendall(b'{"type":"ASSIGN","gpu_indices":[0,0],"gpu_uuids":["x"]}\n')
+    message = json.loads(reader.readline())
+    assert message["type"] == "FAIL" and message["phase"] == "protocol" and "invalid GPU assignment" in message["error"]
+    assert proc.wait(timeout=60) == 1

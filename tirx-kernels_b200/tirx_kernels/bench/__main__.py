@@ -2,8 +2,9 @@
 
 Plain (one-process) mode of the reference CLI (tirx_kernels/bench/__main__.py:357-511):
 same flags, ``BENCH_CONFIGS`` preferred over ``CONFIGS`` (:18-19), result file
-``{"results": [...]}`` and the human line ``OK kernel [label]: impl=...µs``.  The hidden
-prepared-child socket protocol of the reference's bench suite is not provided.
+``{"results": [...]}`` and the human line ``OK kernel [label]: impl=...µs``.  With the hidden flags
+``--prepared-control-fd`` / ``--prepared-num-gpus`` the process instead serves the bench suite's
+prepared-child protocol (:101-354), implemented in ``_prepared_child.py``.
 """
 
 import argparse
@@ -29,6 +30,9 @@ def find_bench_config(module, label: str) -> dict:
 
 
 def main() -> None:
+    import time
+
+    child_started = time.time()
     parser = argparse.ArgumentParser(description="Run kernel benchmarks")
     parser.add_argument("--kernel", type=str, default=None, help="Run only this kernel")
     parser.add_argument("--config", type=str, default=None, help="Run only this config label")
@@ -44,7 +48,19 @@ def main() -> None:
                         help="Also time external library peers (cuBLASLt NVFP4)")
     parser.add_argument("--rounds", type=int, default=None, help="Independent timing rounds")
     parser.add_argument("--cooldown", type=float, default=None, help="Seconds slept before every timing")
+    parser.add_argument("--prepared-control-fd", type=int, default=None, help=argparse.SUPPRESS)
+    parser.add_argument("--prepared-num-gpus", type=int, default=1, help=argparse.SUPPRESS)
     args = parser.parse_args()
+    if args.prepared_num_gpus < 1:
+        print("ERROR: --prepared-num-gpus must be >= 1", file=sys.stderr)
+        sys.exit(2)
+
+    if args.prepared_control_fd is not None:
+        from tirx_kernels.bench import _prepared_child
+        from tirx_kernels.runner import set_external_references_enabled
+
+        set_external_references_enabled(args.with_references)
+        sys.exit(_prepared_child.run(args, find_bench_config, child_started=child_started))
 
     if args.json or args.json_file:
         os.environ["TIRX_BENCH_JSON"] = "1"

@@ -20,7 +20,7 @@ import time
 from collections.abc import Callable, Mapping
 from dataclasses import dataclass, field
 from types import ModuleType
-from typing import Any, Protocol, runtime_checkable
+from typing import Sequence, Any, Protocol, runtime_checkable
 
 DEFAULT_BENCH_ROUNDS = 5
 DEFAULT_BENCH_COOLDOWN_S = 0.0
@@ -121,6 +121,81 @@ class PreparedKernelBenchmark:
     def assert_process_local(self) -> None:
         if os.getpid() != self.owner_pid:
             raise RuntimeError("prepared kernel benchmark used outside its preparing process")
+
+    @property
+    def required_num_gpus(self) -> int:
+        return int(getattr(self.benchmark, "required_num_gpus", 1))
+
+
+# ---- late GPU assignment (the bench suite hands a prepared child its GPU after CPU prepare) ---------
+_ASSIGNMENT: tuple[tuple[int, ...], tuple[str, ...]] | None = None
+
+
+def cuda_is_initialized() -> bool:
+    """True once this process has created a CUDA context through torch (reference runner.py:313-317)."""
+    import sys
+
+    torch = sys.modules.get("torch")
+    return bool(torch is not None and torch.cuda.is_initialized())
+
+
+def canonical_cuda_uuid(value: Any) -> str:
+    text = value.decode() if isinstance(value, bytes) else str(value)
+    text = text.strip().lower()
+    return text[4:] if text.startswith("gpu-") else text
+
+
+def physical_cuda_uuids(device_indices: Sequence[int]) -> tuple[str, ...]:
+    """UUIDs of the given visible device indices, as the driver reports them (reference :347-381)."""
+    import torch
+
+    return tuple(canonical_cuda_uuid(torch.cuda.get_device_properties(int(i)).uuid) for i in device_indices)
+
+
+def bind_cuda_assignment(device_indices: Sequence[int], expected_uuids: Sequence[str]) -> tuple[str, ...]:
+    """Select the late-bound device and prove it is the card the scheduler meant (reference :384-409)."""
+    global _ASSIGNMENT
+    indices = tuple(int(i) for i in device_indices)
+    expected = tuple(canonical_cuda_uuid(u) for u in expected_uuids)
+    if not indices or len(indices) != len(expected) or len(set(indices)) != len(indices):
+        raise ValueError(f"invalid CUDA assignment indices={device_indices!r}, uuids={expected_uuids!r}")
+    import torch
+
+    torch.cuda.set_device(indices[0])
+    actual = physical_cuda_uuids(indices)
+    if actual != expected:
+        raise RuntimeError(f"late GPU assignment identity mismatch: requested {list(expected)}, "
+                           f"physical {list(actual)}")
+    _ASSIGNMENT = (indices, actual)
+    return actual
+
+
+def current_cuda_assignment() -> tuple[tuple[int, ...], tuple[str, ...]]:
+    if _ASSIGNMENT is None:
+        raise RuntimeError("no CUDA assignment is active in this process")
+    return _ASSIGNMENT
+
+
+def current_process_cuda_memory_bytes(device_indices: Sequence[int]) -> dict[int, int | None]:
+    """Device memory this process still holds on each card, from NVML; None where it cannot be read
+    (reference :522-558).  The scheduler uses it to decide whether a card can be handed on."""
+    result: dict[int, int | None] = {int(i): None for i in device_indices}
+    try:
+        import pynvml
+        import torch
+
+        pynvml.nvmlInit()
+        for index in result:
+            uuid = torch.cuda.get_device_properties(index).uuid
+            handle = pynvml.nvmlDeviceGetHandleByUUID(f"GPU-{canonical_cuda_uuid(uuid)}".encode())
+            used = 0
+            for proc in pynvml.nvmlDeviceGetComputeRunningProcesses(handle):
+                if proc.pid == os.getpid():
+                    used = int(proc.usedGpuMemory or 0)
+            result[index] = used
+    except Exception:
+        pass
+    return result
 
 
 # ---- device facts -------------------------------------------------------------------------------
