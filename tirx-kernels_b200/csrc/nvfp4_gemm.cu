@@ -1043,6 +1043,12 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
     const bool pair_ok = M > 128;
     if (!pair_ok) variant = 0;  // decode-sized M: more, narrower tiles (and K ranges) to fill the GPU
     else variant = N % 256 == 0 ? 2 : 3;
+    if (variant == 2) {
+      // few 256 x 256 tiles (fewer than half the CTA pairs busy): 256 x 128 tiles double the parallelism
+      const int sms = device_sm_count();
+      const int64_t tiles = static_cast<int64_t>((M + 255) / 256) * (N / 256);
+      if (sms > 0 && tiles * 2 <= sms / 2) variant = 3;
+    }
   }
   if ((variant == 1 || variant == 2) && N % 256 != 0) {
     set_error("b2_nvfp4_gemm: variant %d needs N %% 256 == 0", variant);
