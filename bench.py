@@ -238,6 +238,7 @@ def cpu_baseline(x_host, gs: float, layout: str, budget_s: float, steps: int | N
 
     import torch
 
+    c_oracle.use_all_host_threads()  # torchrun pins OMP_NUM_THREADS=1 for its ranks
     bits = x_host.contiguous().view(torch.int16).numpy().view(np.uint16)
     m, k = bits.shape
     step_bytes = m * k * 2 + m * k // 2 + nvfp4_oracle.sf_buffer_size(m, k // 16, layout) + 4

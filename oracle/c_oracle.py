@@ -29,8 +29,28 @@ def lib() -> ctypes.CDLL:
     return _LIB
 
 
+def _gomp():
+    lib()  # the oracle library pulls the OpenMP runtime in
+    return ctypes.CDLL("libgomp.so.1")
+
+
 def threads() -> int:
-    return int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+    """Threads the next parallel region will use."""
+    try:
+        return int(_gomp().omp_get_max_threads())
+    except OSError:
+        return int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+
+
+def use_all_host_threads() -> int:
+    """Undo a launcher's OMP_NUM_THREADS=1 (torchrun sets it for every rank): one thread per core this
+    process may run on.  Returns the thread count now in force."""
+    count = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    try:
+        _gomp().omp_set_num_threads(int(count))
+    except OSError:
+        pass
+    return threads()
 
 
 def _p(array: np.ndarray):
