@@ -196,7 +196,7 @@ def record_mufu_tables(out_dir: Path) -> None:
 
 
 def main():
-    out_dir = Path(sys.argv[1] if len(sys.argv) > 1 else "gpurun_out/golden")
+    out_dir = Path(sys.argv[1] if len(sys.argv) > 1 else "golden_out")
     out_dir.mkdir(parents=True, exist_ok=True)
     import flashinfer
 
