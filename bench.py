@@ -36,7 +36,7 @@ sys.path[:0] = [str(REPO / "tirx-kernels_b200"), str(REPO)]
 HEADLINE = {"dtype": "bfloat16", "m": 16384, "k": 7168, "sf_layout": "128x4"}
 METRIC = "nvfp4_quantize HBM throughput (16384x7168 bf16, 128x4 SF, 0.1% outliers); nvfp4_gemm TFLOPS under extra"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel (mean of the two
-# launches in profiles/nvfp4_quantize_bf16_128x4_m16384_k7168.md: 234.95 MB read + ~13.3 MB written
+# launches of the ncu summary kept under profiles/ for this kernel and shape: 234.95 MB read + ~13.3 MB written
 # inside the kernel window; the rest of the 66 MB of output is still dirty in L2 when it ends).
 HEADLINE_DRAM_TRAFFIC_BYTES = 248_232_000
 
