@@ -233,44 +233,52 @@ def compile_kernel(handle, *, arch: str | None = None, cuda_compile_mode: str | 
 
 
 # ---- timing -----------------------------------------------------------------------------------------
-def _chain_ms(fn, n: int, flush) -> float:
-    """Device time per iteration of `n` back-to-back [flush, fn] pairs (either part optional)."""
+def _chain_ms(fn, n: int) -> float:
+    """Device time per iteration of `n` back-to-back launches inside one pair of CUDA events."""
     import torch
 
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(n):
-        if flush is not None:
-            flush.sum()  # a READ of a buffer larger than L2: evicts without leaving dirty lines behind
-        if fn is not None:
-            fn()
+        fn()
     end.record()
     torch.cuda.synchronize()
     return start.elapsed_time(end) / n
 
 
-def _time_one(fn: Callable[[], Any], warmup_ms: float, repeat_ms: float, flush) -> float:
-    """Mean device time of one launch of `fn` in microseconds.
+def _cold_ms(fn, n: int, flush) -> float:
+    """Mean device time of `n` launches, each preceded by an L2 flush and bracketed by its own pair
+    of events.  The flush READS a buffer larger than L2: a write would leave dirty lines whose
+    write-back the timed kernel then pays for.  (Timing [flush, fn] chains and subtracting the flush
+    alone is biased: back-to-back flushes partly hit in L2 and run faster than interleaved ones.)"""
+    import torch
 
-    Launches are timed back to back inside one pair of CUDA events, so the cost of the events
-    themselves is amortised.  With `flush`, every launch is preceded by a read of a buffer
-    larger than L2 (cold cache; a write would leave 126 MB of dirty lines whose write-back the
-    timed kernel then pays for), and the time of the flush alone - measured the same way - is
-    subtracted.
-    """
+    pairs = []
+    for _ in range(n):
+        flush.sum()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        pairs.append((start, end))
+    torch.cuda.synchronize()
+    return sum(a.elapsed_time(b) for a, b in pairs) / n
+
+
+def _time_one(fn: Callable[[], Any], warmup_ms: float, repeat_ms: float, flush) -> float:
+    """Mean device time of one launch of `fn` in microseconds (warm: back-to-back launches between
+    one pair of events; cold: see `_cold_ms`)."""
     import torch
 
     fn()
     torch.cuda.synchronize()
-    estimate_ms = max(_chain_ms(fn, 5, None), 1e-3)
+    estimate_ms = max(_chain_ms(fn, 5), 1e-3)
     n_warmup = max(3, int(warmup_ms / estimate_ms))
     n_repeat = max(10, min(2000, int(repeat_ms / estimate_ms)))
-    _chain_ms(fn, n_warmup, None)
+    _chain_ms(fn, n_warmup)
     if flush is None:
-        return _chain_ms(fn, n_repeat, None) * 1e3
-    both = _chain_ms(fn, n_repeat, flush)
-    alone = _chain_ms(None, n_repeat, flush)
-    return max(both - alone, 0.0) * 1e3
+        return _chain_ms(fn, n_repeat) * 1e3
+    return _cold_ms(fn, min(n_repeat, 500), flush) * 1e3
 
 
 def bench(funcs: Mapping[str, Callable[[], Any]], *, references: Mapping[str, Callable[[], Any]] | None = None,
