@@ -616,6 +616,15 @@ int launch(const RmsParams& p, cudaStream_t stream) {
     if (g_block_owner && (p.H >> 3) == p.vb * TPR && p.vb <= kBlockVb &&
         (reinterpret_cast<uintptr_t>(p.x) & 31) == 0 && (p.H % 16) == 0) {
       constexpr int kP = TPR / kV;
+      // the kernel is instantiated for a few block counts per thread: registers (and with them the CTAs
+      // per SM) follow the row length instead of the maximum
+      if constexpr (kV == 2) {
+        if (p.vb <= 4) return launch_config(rmsnorm_fp4quant_block_kernel<Tag, TPR, BLOCK, 4>, p, 128 / kP, 128, 0, stream);
+        if (p.vb <= 6) return launch_config(rmsnorm_fp4quant_block_kernel<Tag, TPR, BLOCK, 6>, p, 128 / kP, 128, 0, stream);
+        if (p.vb == 7) return launch_config(rmsnorm_fp4quant_block_kernel<Tag, TPR, BLOCK, 7>, p, 128 / kP, 128, 0, stream);
+      } else {
+        if (p.vb <= 2) return launch_config(rmsnorm_fp4quant_block_kernel<Tag, TPR, BLOCK, 2>, p, 128 / kP, 128, 0, stream);
+      }
       return launch_config(rmsnorm_fp4quant_block_kernel<Tag, TPR, BLOCK, kBlockVb>, p, 128 / kP, 128, 0, stream);
     }
     if ((p.H >> 3) == p.vb * TPR && p.vb <= 16) {
