@@ -131,3 +131,56 @@ def test_cluster_reduction_tree_is_restated():
     s = o.rmsnorm_sum_of_squares(x, o.BF16)
     ref = (o.bits_to_f32(x, o.BF16).astype(np.float64) ** 2).sum(-1)
     assert np.allclose(s, ref, rtol=1e-6)
+
+
+def test_add_rmsnorm_configuration_follows_the_reference_thresholds():
+    """_source_config of add_rmsnorm_fp4quant.py :354-363: four row tiles in one CTA, two per cluster CTA."""
+    assert o.add_source_config(16384)["cluster_n"] == 1
+    assert o.add_source_config(16400)["cluster_n"] == 1 and o.add_source_config(16400)["tpr"] == 256
+    for h, n in ((32768, 2), (131072, 4), (262144, 8), (524288, 16)):
+        assert o.add_source_config(h)["cluster_n"] == n
+    assert o.add_source_config(32768)["tpr"] == 128  # the cluster CTAs of this row use 128 threads
+
+
+def test_add_rmsnorm_restatement_is_self_consistent():
+    rng = np.random.default_rng(5)
+    M, H = 5, 512
+    x = o.f32_to_bits(rng.standard_normal((M, H)).astype(np.float32), "bfloat16")
+    r = o.f32_to_bits(rng.standard_normal((M, H)).astype(np.float32), "bfloat16")
+    w = o.f32_to_bits((1 + 0.1 * rng.standard_normal(H)).astype(np.float32), "bfloat16")
+    out = o.add_rmsnorm_fp4quant(x, r, w, "bfloat16", 1.0, 1e-6, swizzled=True)
+    h = o.bits_to_f32(x, "bfloat16") + o.bits_to_f32(r, "bfloat16")
+    assert np.array_equal(out["residual"], o.f32_to_bits(h.astype(np.float32), "bfloat16"))
+    hr = o.bits_to_f32(out["residual"], "bfloat16")
+    want = hr / np.sqrt((h * h).mean(axis=-1, keepdims=True) + 1e-6) * o.bits_to_f32(w, "bfloat16")
+    deq = o.unpack_e2m1(out["y"]).reshape(M, -1, 16) * o.e4m3_decode(out["scale"])[..., None]
+    assert np.abs(deq.reshape(M, H) - want).max() <= 0.5 * np.abs(want).max()
+    assert np.allclose(o.bits_to_f32(out["y_norm"], "bfloat16"), want, rtol=2e-2, atol=2e-2)
+    # the swizzled buffer holds exactly the logical codes
+    assert np.array_equal(o.logical_scales(out["scale_buffer"], M, H // 16, "128x4"), out["scale"])
+    # zero residual and unit weight reduce to the plain block recipe on x * rstd
+    zeros = np.zeros_like(x)
+    ones = o.f32_to_bits(np.ones(H, dtype=np.float32), "bfloat16")
+    plain = o.add_rmsnorm_fp4quant(x, zeros, ones, "bfloat16", 1.0, 1e-6)
+    assert np.array_equal(plain["residual"], x)
+
+
+def test_per_token_restatement_properties():
+    rng = np.random.default_rng(9)
+    m, k = 7, 1040
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[0] = 0.0
+    bits = o.f32_to_bits(x, "float16")
+    packed, sf, token = o.nvfp4_quantize_per_token(bits, "float16", 1.0 / 2688.0, "128x4")
+    assert token[0] == 0.0 and not packed[0].any()
+    amax = np.abs(o.bits_to_f32(bits, "float16")).max(axis=-1)
+    assert np.array_equal(token[1:], (amax[1:] * np.float32(1.0 / 2688.0)).astype(np.float32))
+    # scaling a row by two doubles its token scale and leaves its codes unchanged
+    bits2 = o.f32_to_bits(2.0 * o.bits_to_f32(bits, "float16"), "float16")
+    packed2, sf2, token2 = o.nvfp4_quantize_per_token(bits2, "float16", 1.0 / 2688.0, "128x4")
+    assert np.array_equal(token2, 2.0 * token)
+    same = np.mean(packed2 == packed)
+    assert same > 0.99  # rcp.approx of the doubled scale may move a handful of codes by one step
+    # padding columns (65 -> 68) and padding rows (7 -> 128) of the swizzled buffer are zero
+    logical = o.logical_scales(sf, m, k // 16, "128x4")
+    assert sf.sum() == logical.sum()
