@@ -141,10 +141,12 @@ class PeerOutputBuffers:
             self._own = 0
 
 
-def fused_forward(proj: ShardedProjection, act, buffers: PeerOutputBuffers, barrier: Callable | None = None):
+def fused_forward(proj: ShardedProjection, act, buffers: PeerOutputBuffers, barrier: Callable | None = None,
+                  launch: Callable | None = None):
     """Quantize, then GEMM with the all-gather done by the GEMM's own epilogue over peer stores.
 
-    Returns the row-major ``[M, N]`` tensor on this GPU.  `barrier()` must order every rank's GEMM
+    Returns the row-major ``[M, N]`` tensor on this GPU.  `launch` defaults to the fused kernel
+    (``b2_nvfp4_gemm_allgather``).  `barrier()` must order every rank's GEMM
     before any rank's read (default: a one-element NCCL all-reduce on the current stream).  A caller
     that runs steps back to back alternates between two `PeerOutputBuffers`, so that a fast rank's
     next step cannot overwrite rows a slow rank is still reading.
@@ -152,8 +154,9 @@ def fused_forward(proj: ShardedProjection, act, buffers: PeerOutputBuffers, barr
     from .. import _native
 
     A_fp4, A_sf = proj.quantize(act)
-    _native.nvfp4_gemm_allgather(A_fp4, proj.B_fp4, A_sf, proj.B_sf, proj.alpha, buffers.addresses,
-                                 proj.rank, proj.m, proj.shard, proj.k)
+    if launch is None:  # `launch` lets a CPU test stand in for the kernel, as `quantize` / `gemm` do above
+        launch = _native.nvfp4_gemm_allgather
+    launch(A_fp4, proj.B_fp4, A_sf, proj.B_sf, proj.alpha, buffers.addresses, proj.rank, proj.m, proj.shard, proj.k)
     if proj.world > 1:
         if barrier is None:
             import torch
