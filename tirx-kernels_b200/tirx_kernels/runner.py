@@ -7,9 +7,15 @@ uses - ``run_kernel_test`` (:744-761), ``run_kernel_bench`` (:764-798), the two-
 ``hardware_num_sms`` (:320-334) - and drops everything that only exists to drive TVM.
 
 Timing.  The reference delegates to ``tvm.tirx.bench.bench`` (Proton by default).  Here
-``bench`` times with CUDA events on the current stream, after a warm-up budget, zeroing a
-256 MiB buffer before every timed launch so each launch starts with a cold L2 - the same
-conditions as the reference's protocol (25 ms warm-up, 100 ms repeat, 5 rounds, mean).
+``bench`` times with CUDA events on the current stream after a warm-up budget.  Timer
+``event`` (default) brackets every launch with its own pair of events and reads a 256 MiB
+buffer before it, so each launch starts with a cold, clean L2 - the conditions of the
+reference's protocol (25 ms warm-up, 100 ms repeat, 5 rounds, mean); launches of a few
+microseconds also carry the host's launch latency in this mode.  Timer ``event_warm`` times
+back-to-back launches between one pair of events.
+
+Late GPU assignment (``bind_cuda_assignment`` and friends, reference :347-449, :522-558)
+serves the bench suite's prepared-child protocol, see ``bench/_prepared_child.py``.
 """
 
 from __future__ import annotations
