@@ -44,6 +44,10 @@ extern "C" {
 #define B2_MUFU_LG2 2       /* lg2.approx.f32       */
 #define B2_MUFU_EX2 3       /* ex2.approx.f32       */
 #define B2_MUFU_EX2_FTZ 4   /* ex2.approx.ftz.f32   */
+/* The quantizer's SiLU on one fp32 value: as the kernel computes it (packed-FMA division with a
+ * div.rn.f32 fallback) and with div.rn.f32 throughout; the two must agree bit for bit. */
+#define B2_PROBE_SILU 5
+#define B2_PROBE_SILU_DIV_RN 6
 
 /* Reason for the most recent non-zero status returned to this thread. */
 const char* b2_last_error(void);

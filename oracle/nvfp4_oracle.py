@@ -258,13 +258,19 @@ def sf_buffer_size(m: int, sf_cols: int, layout: str) -> int:
 # --------------------------------------------------------------------------------------
 # nvfp4_quantize  (tirx_kernels/flashinfer/quantization/nvfp4_quantize.py)
 # --------------------------------------------------------------------------------------
-def silu_and_mul(gate_bits, up_bits, dtype: str, mufu) -> np.ndarray:
-    """fp_quant.py silu_f32 :340-344 and silu_and_mul_pair :363-372; returns uint16 storage."""
-    g = bits_to_f32(gate_bits, dtype)
-    u = bits_to_f32(up_bits, dtype)
+def silu_f32(g: np.ndarray, mufu) -> np.ndarray:
+    """fp_quant.py silu_f32 :340-344: mul.f32 by -log2(e), ex2.approx.ftz.f32, add.f32 of 1.0, div.rn.f32."""
+    g = np.asarray(g, dtype=np.float32)
     e = mufu.ex2_ftz(g * np.float32(-1.4426950408889634))
     with np.errstate(over="ignore", invalid="ignore", divide="ignore"):
-        s = g / (e + np.float32(1.0))
+        return (g / (e + np.float32(1.0))).astype(np.float32)
+
+
+def silu_and_mul(gate_bits, up_bits, dtype: str, mufu) -> np.ndarray:
+    """fp_quant.py silu_and_mul_pair :363-372; returns uint16 storage."""
+    u = bits_to_f32(up_bits, dtype)
+    s = silu_f32(bits_to_f32(gate_bits, dtype), mufu)
+    with np.errstate(over="ignore", invalid="ignore"):
         return f32_to_bits((s * u).astype(np.float32), dtype)
 
 

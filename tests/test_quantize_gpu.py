@@ -95,3 +95,24 @@ def test_invalid_arguments_are_rejected_before_launch(native):
         native.nvfp4_quantize(x, out, sf, gs, 4, 24, "float16", "linear")
     with pytest.raises(ValueError, match="m=0"):
         native.nvfp4_quantize(x, out, sf, gs, 0, 32, "float16", "linear")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_silu_fast_division_equals_div_rn_on_every_input(dtype, native):
+    """The SiLU-fused quantizer divides with packed FMAs where that is exact and with div.rn.f32 elsewhere.
+    A gate is a 16-bit value, so the whole input domain is 65536 values per dtype: all of them, NaNs,
+    infinities, zeros of both signs and subnormals included, must give div.rn.f32's bits, and those must
+    be the oracle's (mul.f32, ex2.approx.ftz from the device, add.f32, IEEE division)."""
+    import oracle_provider
+    from oracle import nvfp4_oracle
+
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16)
+    gates = bits.view(dtype).float().numpy()
+    fast = native.mufu_probe("silu", gates)
+    exact = native.mufu_probe("silu_div_rn", gates)
+    assert np.array_equal(fast.view(np.uint32), exact.view(np.uint32))
+    mufu = oracle_provider.probe_mufu(native)
+    finite = np.isfinite(gates)
+    with np.errstate(all="ignore"):
+        want = nvfp4_oracle.silu_f32(gates[finite], mufu)
+    assert np.array_equal(exact[finite].view(np.uint32), np.asarray(want, dtype=np.float32).view(np.uint32))

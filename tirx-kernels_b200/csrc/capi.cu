@@ -56,6 +56,8 @@ __global__ void mufu_probe_kernel(int op, const float* __restrict__ in, float* _
     case B2_MUFU_RSQRT_FTZ: r = rsqrt_approx_ftz(x); break;
     case B2_MUFU_LG2: r = lg2_approx(x); break;
     case B2_MUFU_EX2: r = ex2_approx(x); break;
+    case B2_PROBE_SILU: r = silu_f32x2<false>(make_float2(x, x)).x; break;
+    case B2_PROBE_SILU_DIV_RN: r = silu_f32x2<true>(make_float2(x, x)).x; break;
     default: r = ex2_approx_ftz(x); break;
   }
   out[i] = r;
@@ -70,7 +72,7 @@ extern "C" int b2_abi_version(void) { return 1; }
 
 extern "C" int b2_mufu_probe(int op, const float* in_dev, float* out_dev, int n, void* stream) {
   using namespace b2;
-  if (op < B2_MUFU_RCP_FTZ || op > B2_MUFU_EX2_FTZ) {
+  if (op < B2_MUFU_RCP_FTZ || op > B2_PROBE_SILU_DIV_RN) {
     set_error("b2_mufu_probe: unknown op %d", op);
     return B2_ERR_INVALID_ARGUMENT;
   }

@@ -13,7 +13,9 @@ from pathlib import Path
 DTYPE_CODES = {"float16": 0, "bfloat16": 1}
 SF_LAYOUT_CODES = {"linear": 0, "128x4": 1, "8x4": 2}
 SCALE_FORMAT_CODES = {"e4m3": 0, "ue8m0": 1}
-MUFU_OPS = {"rcp_ftz": 0, "rsqrt_ftz": 1, "lg2": 2, "ex2": 3, "ex2_ftz": 4}
+MUFU_OPS = {"rcp_ftz": 0, "rsqrt_ftz": 1, "lg2": 2, "ex2": 3, "ex2_ftz": 4,
+            # the quantizer's SiLU as its kernel computes it / with div.rn.f32 throughout
+            "silu": 5, "silu_div_rn": 6}
 
 OK, ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_UNSUPPORTED = range(5)
 
