@@ -22,16 +22,18 @@ def variant(native):
 
 
 SMALL_SHAPES = [(128, 128, 256), (256, 256, 256), (384, 640, 768), (1024, 1024, 1024), (16, 512, 2048),
-                (200, 384, 512)]
+                (200, 384, 512), (1, 256, 4096), (32, 1024, 8192), (7, 768, 2304)]
 
 
-@pytest.mark.parametrize("which", [0, 1, 2, 3])
+@pytest.mark.parametrize("which", [0, 1, 2, 3, 4, 5])
 @pytest.mark.parametrize("M,N,K", SMALL_SHAPES)
 def test_every_variant_matches_the_oracle(which, M, N, K, variant, native):
     import oracle_provider
 
-    if which in (1, 2) and N % 256:
+    if which in (1, 2, 5) and N % 256:
         pytest.skip("variant needs N % 256 == 0")
+    if which in (4, 5) and M > 32:
+        pytest.skip("variant needs M <= 32")
     mod = _module()
     A_fp4, B_fp4, A_sf, B_sf, alpha, _ = mod.prepare_data(M, N, K)
     alpha_t = torch.tensor([float(alpha)], device="cuda")
@@ -44,6 +46,25 @@ def test_every_variant_matches_the_oracle(which, M, N, K, variant, native):
                                               alpha=float(alpha_t.item())))
     assert torch.isfinite(out.float()).all()
     assert mod.relative_frobenius_error(out.cpu(), want) <= TOLERANCE
+
+
+@pytest.mark.parametrize("wide", [0, 1])
+def test_short_a_ring_equals_the_full_one_bit_for_bit(wide, variant, native):
+    """For M <= 32 only 32 rows of A are loaded per stage (the MMA's other rows read whatever follows in
+    shared memory and land in accumulator rows nobody reads): same products, same order, same bits."""
+    mod = _module()
+    M, N, K = 20, 1024, 4096
+    A_fp4, B_fp4, A_sf, B_sf, alpha, _ = mod.prepare_data(M, N, K)
+    alpha_t = torch.tensor([float(alpha)], device="cuda")
+    outs = []
+    for which in (wide, wide + 4):
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        variant(which)
+        native.nvfp4_gemm(A_fp4, B_fp4, A_sf, B_sf, alpha_t, out, M, N, K)
+        torch.cuda.synchronize()
+        native.nvfp4_gemm_status()
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
 
 
 @pytest.mark.parametrize("label", ["1024x1024x1024", "2048x2048x2048", "384x640x768", "16x8192x8192",

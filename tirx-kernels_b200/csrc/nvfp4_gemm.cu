@@ -250,11 +250,15 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
 }
 
 // ---- shared memory ------------------------------------------------------------------------------
-template <int CG, int BN, int STAGES, int TMA_OUT = 0>
+// AM: rows of A the TMA writes per stage.  The MMA always reads 128 rows; with AM < 128 (M <= AM) the
+// rows past AM are whatever follows in the stage, which only reaches accumulator rows nobody reads,
+// and the shared memory saved buys more stages in flight.
+template <int CG, int BN, int STAGES, int TMA_OUT = 0, int AM = kBlockM>
 struct SmemLayout {
   static constexpr int kBRows = BN / CG;                       // rows of B held by one CTA
   static constexpr int kChunks = BN / 128 > 0 ? BN / 128 : 1;  // 128-row scale chunks of B
-  static constexpr int kABytes = kBlockM * 128;
+  static constexpr int kABytes = AM * 128;
+  static_assert(AM == kBlockM || (CG == 1 && kABytes + BN * 128 >= kBlockM * 128), "the MMA's 128-row window stays inside the stage");
   static constexpr int kBBytes = kBRows * 128;
   static constexpr int kSfaBytes = 4 * 512;                    // 4 K-blocks of 64, 512 B each
   static constexpr int kSfbBytes = kChunks * 4 * 512;
@@ -350,12 +354,12 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-template <int CG, int BN, int STAGES, int TMA_OUT>
+template <int CG, int BN, int STAGES, int TMA_OUT, int AM>
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                       const __grid_constant__ GemmParams p, const __grid_constant__ OutMaps<(TMA_OUT > 0)> out_maps) {
-  using L = SmemLayout<CG, BN, STAGES, TMA_OUT>;
+  using L = SmemLayout<CG, BN, STAGES, TMA_OUT, AM>;
   constexpr int kTmemCols = 512;
   constexpr uint32_t kIdesc = instr_desc(kBlockM * CG, BN);
   constexpr uint32_t kOperandTx = static_cast<uint32_t>(L::kABytes + L::kBBytes) * CG;
@@ -823,11 +827,11 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, const fl
   *reinterpret_cast<uint4*>(D + i) = out;
 }
 
-template <int CG, int BN, int STAGES>
+template <int CG, int BN, int STAGES, int AM = kBlockM>
 int encode_maps(MapSet* maps, const void* A, const void* B, const void* SFA, const void* SFB, int M, int N, int K) {
-  using L = SmemLayout<CG, BN, STAGES>;
+  using L = SmemLayout<CG, BN, STAGES, 0, AM>;
   const int m_padded = (M + 127) / 128 * 128, n_padded = (N + 127) / 128 * 128;
-  if (int rc = encode_operand_map(&maps->a, A, M, K, kBlockM)) return rc;
+  if (int rc = encode_operand_map(&maps->a, A, M, K, AM)) return rc;
   if (int rc = encode_operand_map(&maps->b, B, N, K, L::kBRows)) return rc;
   if (int rc = encode_scale_map(&maps->sfa, SFA, m_padded, K, 1)) return rc;
   if (int rc = encode_scale_map(&maps->sfb, SFB, n_padded, K, L::kChunks)) return rc;
@@ -857,12 +861,12 @@ int encode_output_map(CUtensorMap* map, void* base, int M, int ldd) {
   return B2_OK;
 }
 
-template <int CG, int BN, int STAGES, int TMA_OUT = 0>
+template <int CG, int BN, int STAGES, int TMA_OUT = 0, int AM = kBlockM>
 int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N, int K, int splits,
                    uint32_t* status, float* partial, cudaStream_t stream, const GatherTarget& gather = GatherTarget(),
                    const OutMaps<(TMA_OUT > 0)>& out_maps = OutMaps<(TMA_OUT > 0)>()) {
-  using L = SmemLayout<CG, BN, STAGES, TMA_OUT>;
-  auto kernel = nvfp4_gemm_kernel<CG, BN, STAGES, TMA_OUT>;
+  using L = SmemLayout<CG, BN, STAGES, TMA_OUT, AM>;
+  auto kernel = nvfp4_gemm_kernel<CG, BN, STAGES, TMA_OUT, AM>;
   GemmParams p;
   p.alpha = alpha;
   p.D = static_cast<uint16_t*>(D);
@@ -950,7 +954,7 @@ int choose_splits(int tiles, int k_slabs, int units_available) {
   return splits;
 }
 
-template <int CG, int BN, int STAGES, int TMA_OUT = 0>
+template <int CG, int BN, int STAGES, int TMA_OUT = 0, int AM = kBlockM>
 int launch_variant(const void* A, const void* B, const void* SFA, const void* SFB, const float* alpha,
                    void* D, int M, int N, int K, int variant, cudaStream_t stream) {
   uint32_t* status = nullptr;
@@ -962,7 +966,7 @@ int launch_variant(const void* A, const void* B, const void* SFA, const void* SF
     auto it = g_maps.find(key);
     if (it == g_maps.end()) {
       MapSet fresh;
-      if (int rc = encode_maps<CG, BN, STAGES>(&fresh, A, B, SFA, SFB, M, N, K)) return rc;
+      if (int rc = encode_maps<CG, BN, STAGES, AM>(&fresh, A, B, SFA, SFB, M, N, K)) return rc;
       if (g_maps.size() > 4096) g_maps.clear();
       it = g_maps.emplace(key, fresh).first;
     }
@@ -994,7 +998,7 @@ int launch_variant(const void* A, const void* B, const void* SFA, const void* SF
     return launch_kernels<CG, BN, STAGES, TMA_OUT>(maps, alpha, D, M, N, K, splits, status, partial, stream, target,
                                                 out_maps);
   } else {
-    return launch_kernels<CG, BN, STAGES>(maps, alpha, D, M, N, K, splits, status, partial, stream);
+    return launch_kernels<CG, BN, STAGES, 0, AM>(maps, alpha, D, M, N, K, splits, status, partial, stream);
   }
 }
 
@@ -1005,9 +1009,10 @@ int g_forced_variant = -1;  // test hook: -1 = automatic
 
 // Selects a kernel variant for the following calls of this process (-1 restores automatic
 // selection).  0: single CTA, N tile 128; 1: single CTA, N tile 256; 2: CTA pair, N tile 256;
-// 3: CTA pair, N tile 128.  Used by the tests to exercise every variant on small shapes.
+// 3: CTA pair, N tile 128; 4 and 5: 0 and 1 for M <= 32, loading 32 rows of A per stage into a deeper
+// ring.  Used by the tests to exercise every variant on small shapes.
 extern "C" int b2_nvfp4_gemm_set_variant(int variant) {
-  if (variant < -1 || variant > 3) {
+  if (variant < -1 || variant > 5) {
     b2::set_error("b2_nvfp4_gemm_set_variant: unknown variant %d", variant);
     return B2_ERR_INVALID_ARGUMENT;
   }
@@ -1041,7 +1046,23 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
   int variant = g_forced_variant;
   if (variant < 0) {
     const bool pair_ok = M > 128;
-    if (!pair_ok) variant = 0;  // decode-sized M: more, narrower tiles (and K ranges) to fill the GPU
+    if (!pair_ok) {
+      // Decode-sized M: single-CTA tiles and K ranges to fill the GPU.  The time goes with the slabs
+      // one CTA runs in series (waves x slabs per work item); a 256-wide slab costs about 1.8 of a
+      // 128-wide one, and its four-fold partial sums only pay off while M is small.
+      variant = 0;
+      const int sms = device_sm_count();
+      if (sms > 0 && M <= 32 && N % 256 == 0) {
+        const int k_slabs = K / kBlockK;
+        auto serial_slabs = [&](int bn) {
+          const int tiles = N / bn;
+          const int splits = choose_splits(tiles, k_slabs, sms);
+          return static_cast<double>((tiles * splits + sms - 1) / sms) * (k_slabs / splits);
+        };
+        if (1.8 * serial_slabs(256) < serial_slabs(128)) variant = 1;
+      }
+      if (M <= 32) variant += 4;  // 32 rows of A per stage, deeper ring
+    }
     else variant = N % 256 == 0 ? 2 : 3;
     if (variant == 2) {
       // few 256 x 256 tiles (fewer than half the CTA pairs busy): 256 x 128 tiles double the parallelism
@@ -1050,7 +1071,11 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
       if (sms > 0 && tiles * 2 <= sms / 2) variant = 3;
     }
   }
-  if ((variant == 1 || variant == 2) && N % 256 != 0) {
+  if ((variant == 4 || variant == 5) && M > 32) {
+    set_error("b2_nvfp4_gemm: variant %d needs M <= 32", variant);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  if ((variant == 1 || variant == 2 || variant == 5) && N % 256 != 0) {
     set_error("b2_nvfp4_gemm: variant %d needs N %% 256 == 0", variant);
     return B2_ERR_INVALID_ARGUMENT;
   }
@@ -1058,6 +1083,8 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
     case 0: return launch_variant<1, 128, 6>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 0, s);
     case 1: return launch_variant<1, 256, 4>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 1, s);
     case 2: return launch_variant<2, 256, 5, 1>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 2, s);
+    case 4: return launch_variant<1, 128, 9, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 4, s);
+    case 5: return launch_variant<1, 256, 5, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 5, s);
     default: return launch_variant<2, 128, 6, 1>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
   }
 }
