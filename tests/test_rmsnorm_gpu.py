@@ -105,3 +105,23 @@ def test_invalid_arguments_are_rejected_before_launch(native):
     for bad in (dict(H=32), dict(H=4104, block_size=32), dict(block_size=8), dict(scale_format="e5m2"), dict(M=0)):
         with pytest.raises(ValueError):
             mod.get_kernel(**{**base, **bad})
+
+
+@pytest.mark.parametrize("dtype,H,block,M,swizzled", [
+    ("bfloat16", 7168, 16, 8193, True),
+    ("float16", 8192, 16, 6001, False),
+    ("bfloat16", 4096, 16, 9601, True),
+    ("float16", 2048, 16, 9603, False),
+    ("bfloat16", 1024, 16, 20005, True),
+    ("bfloat16", 1024, 32, 40007, False),
+    ("float16", 512, 16, 19203, True),
+])
+def test_many_ragged_rows_stay_bit_exact(dtype, H, block, M, swizzled, oracle_expected):
+    """Several generations of CTAs per SM (the look-ahead prefetch reaches past the end of the input for the
+    last of them), odd row counts so that the last CTA holds fewer rows than it has room for; every block
+    count per thread of the block-owner kernel and both block sizes appear."""
+    from tirx_kernels.flashinfer.norm import rmsnorm_fp4quant as mod
+
+    cfg = mod._cfg("manyrows", dtype, H, M=M, block_size=block, scale_format="e4m3" if block == 16 else "ue8m0",
+                   swizzled=swizzled, global_scale_mode="computed" if block == 16 else "none")
+    mod.run_test(**cfg)
