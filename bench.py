@@ -352,6 +352,16 @@ def extras(args, rank: int, world: int, distributed: bool) -> dict:
             "timing": "CUDA graph of 12 launches rotating over 4 buffer sets (cold inputs)",
             "roofline": _checks.roofline_hbm(rms.algorithmic_bytes(8192, 7168, 16, True), us_graph)}
         del rsets, rlaunches
+        # the same kernel on 32768 rows (470 MB input, cold by size): the launch-size-independent rate
+        big = dict(cfg)
+        big["M"] = 32768
+        dbig, obig = rms._prepare_tensors(big), rms._prepare_output(big, initialize=False)
+        exr_big = rms.get_kernel(**{kk: v for kk, v in big.items() if kk != "label"}).config["launcher"]
+        us_big = _graph_us([lambda: rms._launch(exr_big, dbig, obig, big)] * 4)
+        out["rmsnorm_fp4quant_bf16_m32768_h7168_swizzled"] = {
+            "us": us_big, "timing": "CUDA graph of 4 launches",
+            "roofline": _checks.roofline_hbm(rms.algorithmic_bytes(32768, 7168, 16, True), us_big)}
+        del dbig, obig
 
         # residual add + RMSNorm + quantize 8192 x 7168 (385 MB per launch > L2)
         from tirx_kernels.flashinfer.norm import add_rmsnorm_fp4quant as addrms
