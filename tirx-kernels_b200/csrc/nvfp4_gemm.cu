@@ -417,6 +417,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   if constexpr (CG == 2) cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // With K ranges a second kernel adds the partial sums: let it launch now and wait, resident, for this
+  // grid to finish, instead of paying its launch after the last CTA has left.
+  if (p.splits > 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == kWarpProducer) {
     // ================= TMA producer =================
@@ -806,6 +809,7 @@ int status_word(uint32_t** out) {
 // D = bf16(alpha * sum over K ranges of the fp32 partial sums), ranges added in index order.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ alpha,
                                      uint16_t* __restrict__ D, int64_t mn, int splits) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the GEMM grid has finished and its partial sums are visible
   const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
   if (i >= mn) return;
   float acc[8];
@@ -911,8 +915,16 @@ int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N
     const int64_t mn = static_cast<int64_t>(M) * N;
     const int threads = 256;
     const int64_t blocks = (mn / 8 + threads - 1) / threads;
-    splitk_reduce_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(partial, alpha, p.D, mn, splits);
-    B2_CUDA_TRY(cudaGetLastError());
+    cudaLaunchConfig_t rcfg = {};
+    rcfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    rcfg.blockDim = dim3(threads);
+    rcfg.stream = stream;
+    cudaLaunchAttribute rattr[1];
+    rattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    rattr[0].val.programmaticStreamSerializationAllowed = 1;
+    rcfg.attrs = rattr;
+    rcfg.numAttrs = 1;
+    B2_CUDA_TRY(cudaLaunchKernelEx(&rcfg, splitk_reduce_kernel, static_cast<const float*>(partial), alpha, p.D, mn, splits));
   }
   return B2_OK;
 }
