@@ -137,7 +137,20 @@ int b2_add_rmsnorm_fp4quant(const void* x, void* residual, const void* w, void* 
  *              ceil(M/128)*128 x K/16 and ceil(N/128)*128 x K/16 bytes
  *   alpha_dev  device fp32 scalar (1 / (encode scale of A * encode scale of B))
  * Requirements: K % 256 == 0, N % 128 == 0, M >= 1, all pointers 16-byte aligned.
- * Tensor maps are cached per (pointers, shape) inside the library.
+ * Tensor maps are cached per (pointers, shape) inside the library (host memory).
+ *
+ * Device memory the library allocates on the caller's behalf, and when (the reference's executable
+ * allocates nothing; a caller that must not allocate uses b2_nvfp4_gemm_small_m_noalloc):
+ *  - 256 bytes of status words per device, on the first GEMM call on that device;
+ *  - for M <= 128 (the problem is cut into K ranges whose fp32 partial sums a second kernel adds):
+ *    one scratch buffer per device, 32 MiB on the first such call, replaced by a larger one only
+ *    when a later problem needs more (K ranges x M x N x 4 bytes).  An outgrown buffer is kept
+ *    until the process exits, never freed, so launches in flight and captured graphs that name it
+ *    stay valid and no call takes the device-wide synchronisation of cudaFree.
+ * Consequences for M <= 128: make the first call of a shape class before any stream capture (a call
+ * that allocates inside a capture invalidates it); calls on one device share the scratch, so keep
+ * them in stream order - two such calls that overlap on the GPU (different streams, graphs
+ * replayed concurrently) race on it.
  */
 int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, const void* SFB,
                   const float* alpha_dev, void* D, int M, int N, int K, void* stream);
@@ -156,7 +169,8 @@ int b2_nvfp4_gemm_status(void* stream);
 
 /*
  * Decode-sized GEMM (1 <= M <= 128) for callers that must not allocate device memory.  It has no
- * counterpart in the reference.  Same operands and result as b2_nvfp4_gemm, but neither this call
+ * counterpart in the reference.  Same operands, kernel variant, K ranges and therefore the same bits
+ * of the result as b2_nvfp4_gemm, but neither this call
  * nor its first-use set-up calls cudaMalloc, cudaFree or any allocating library routine: the
  * partial sums of its split-K path and its status words live in a 4 MiB + 256 B array built
  * into the library (resident on every GPU that loads it until the process exits).
@@ -169,11 +183,31 @@ int b2_nvfp4_gemm_status(void* stream);
  *    B2_ERR_INVALID_ARGUMENT; b2_last_error() states the requirement and the limit.
  *  - All calls on a device share the array: keep them in stream order, calls that overlap on the
  *    GPU race on it.  Nothing has to be cleared between calls.
- *  - Expired bounded waits end the kernel cleanly but are not reported through
- *    b2_nvfp4_gemm_status.
+ *  - Expired bounded waits end the kernel cleanly and are reported by
+ *    b2_nvfp4_gemm_small_m_noalloc_status (not by b2_nvfp4_gemm_status, which reads the words of
+ *    the allocating entry point).
  */
 int b2_nvfp4_gemm_small_m_noalloc(const void* A, const void* B, const void* SFA, const void* SFB,
                                   const float* alpha_dev, void* D, int M, int N, int K, void* stream);
+
+/* Reads (and clears) the status words b2_nvfp4_gemm_small_m_noalloc's kernels write on the current
+ * device; synchronises `stream` first.  Returns B2_OK, or B2_ERR_DEVICE_TIMEOUT with the detail in
+ * b2_last_error().  Allocates nothing (an 8-byte copy out of the built-in array).  No counterpart in
+ * the reference. */
+int b2_nvfp4_gemm_small_m_noalloc_status(void* stream);
+
+/*
+ * Test hooks of the device-side bounded waits (the reference has no analogue: its kernels wait
+ * without a limit).  b2_nvfp4_gemm_set_wait_budget_ms shortens the budget of every wait in later
+ * GEMM launches of this process to `milliseconds` (0 restores the default of one second; waits
+ * downstream of a stalled role get twice the budget so that the status names the role that stalled
+ * first).  b2_nvfp4_gemm_inject_test_fault(1) makes the NEXT launch announce, for the first K slab
+ * of CTA 0, 16 bytes more than its copies deliver: every copy still lands and nothing stays in
+ * flight, but the slab's barrier never completes, the MMA role's wait runs out, the kernel ends
+ * through its abort path and b2_nvfp4_gemm_status reports B2_ERR_DEVICE_TIMEOUT.  Off by default.
+ */
+int b2_nvfp4_gemm_set_wait_budget_ms(int milliseconds);
+int b2_nvfp4_gemm_inject_test_fault(int fault);
 
 /*
  * Column-sharded projection with its output all-gather fused into the GEMM epilogue, for the

@@ -654,15 +654,31 @@ def dequantize_mxfp4(packed, sf, layout: str, block_size: int = 32) -> np.ndarra
     return (vals.reshape(m, -1, block_size) * scales[..., None]).reshape(m, k).astype(np.float32)
 
 
-def nvfp4_gemm(a_packed, b_packed, a_sf, b_sf, alpha) -> np.ndarray:
+def dequantize_nvfp4_rows(packed, sf, rows, block_size: int = 16) -> np.ndarray:
+    """Rows `rows` of dequantize_nvfp4(packed, sf, "128x4"): only those rows are decoded."""
+    rows = np.asarray(rows, dtype=np.int64)
+    vals = unpack_e2m1(np.asarray(packed, dtype=np.uint8)[rows])
+    k = vals.shape[1]
+    sf_cols = k // block_size
+    off = sf_offsets("128x4", rows[:, None], np.arange(sf_cols)[None, :], padded_sf_cols(sf_cols))
+    scales = e4m3_decode(np.asarray(sf, dtype=np.uint8).reshape(-1)[off])
+    return (vals.reshape(len(rows), -1, block_size) * scales[..., None]).reshape(len(rows), k).astype(np.float32)
+
+
+def nvfp4_gemm(a_packed, b_packed, a_sf, b_sf, alpha, rows=None) -> np.ndarray:
     """D = bf16(alpha * A_deq @ B_deq^T) with fp32 accumulation; returns bf16 storage (uint16).
 
     Semantics of tirx_kernels/basic/nvfp4_gemm.py: block-scaled operands :694-719, alpha then
-    bf16 in the epilogue :795-800; data contract prepare_data :47-66.
+    bf16 in the epilogue :795-800; data contract prepare_data :47-66.  With `rows` (indices into
+    A) only those output rows are computed, which keeps problems of 8192^3 and beyond within
+    seconds of CPU time while every sampled row is still a full-length dot product.
     """
     import torch
 
-    a = torch.from_numpy(dequantize_nvfp4(a_packed, a_sf, "128x4"))
+    if rows is None:
+        a = torch.from_numpy(dequantize_nvfp4(a_packed, a_sf, "128x4"))
+    else:
+        a = torch.from_numpy(dequantize_nvfp4_rows(a_packed, a_sf, rows))
     b = torch.from_numpy(dequantize_nvfp4(b_packed, b_sf, "128x4"))
     d = torch.mm(a, b.t()) * float(np.float32(alpha))
     return d.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)

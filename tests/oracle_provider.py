@@ -65,7 +65,11 @@ def make_provider(native, *, prefer_c: bool = True):
 
 
 def gemm_expected(kw) -> torch.Tensor:
-    """bf16 D of dequantize-then-fp32-matmul on the very bytes the kernel consumed."""
+    """bf16 D of dequantize-then-fp32-matmul on the very bytes the kernel consumed; with
+    kw["rows"] (row indices of A) only those rows of D."""
+    rows = kw.get("rows")
+    if rows is not None:
+        rows = np.asarray(torch.as_tensor(rows).cpu().numpy(), dtype=np.int64)
     bits = nvfp4_oracle.nvfp4_gemm(kw["A_fp4"].cpu().numpy(), kw["B_fp4"].cpu().numpy(),
-                                   kw["A_sf"].cpu().numpy(), kw["B_sf"].cpu().numpy(), kw["alpha"])
+                                   kw["A_sf"].cpu().numpy(), kw["B_sf"].cpu().numpy(), kw["alpha"], rows=rows)
     return torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16)

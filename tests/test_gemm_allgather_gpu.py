@@ -24,7 +24,7 @@ def _module():
 
 @pytest.mark.parametrize("world,M,N,K", [(2, 256, 512, 512), (4, 384, 1024, 768), (2, 200, 256, 256),
                                          (1, 256, 256, 256)])
-def test_ranks_in_sequence_fill_every_buffer(world, M, N, K, native):
+def test_ranks_in_sequence_fill_every_buffer(world, M, N, K, native, oracle_expected):
     from tirx_kernels.basic import ffn_tp
 
     mod = _module()
@@ -42,6 +42,8 @@ def test_ranks_in_sequence_fill_every_buffer(world, M, N, K, native):
     native.nvfp4_gemm_status()
     for b in buffers:
         assert torch.equal(b, full)
+    # and the gathered rows themselves against the oracle, not only against the plain GEMM
+    mod.check_output(buffers[-1], A_fp4, B_fp4, A_sf, B_sf, float(alpha_t.item()))
 
 
 def test_rejects_what_it_cannot_run(native):
@@ -89,7 +91,19 @@ def _two_gpu_worker(rank: int, world: int, port: int, M: int, N: int, K: int, re
         out = ffn_tp.fused_forward(proj, None, buffers)
         torch.cuda.synchronize()
         _native.nvfp4_gemm_status()
-        results[rank] = bool(torch.equal(out, full))
+        # the gathered result against the oracle (sampled rows beyond its size limit) and the device-side
+        # fp32 checker, then against the plain GEMM bit for bit
+        import sys
+        from pathlib import Path
+
+        sys.path.insert(0, str(Path(__file__).resolve().parent))
+        sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+        import oracle_provider
+        from tirx_kernels import runner
+
+        runner.set_reference_provider(oracle_provider.make_provider(_native))
+        errors = mod.check_output(out, A_fp4, B_fp4, A_sf, B_sf, float(alpha_t.item()))
+        results[rank] = bool(torch.equal(out, full)) and errors["rel_fro_vs_oracle"] <= 2e-3
         dist.barrier()
         buffers.close()
     finally:

@@ -184,3 +184,35 @@ def test_per_token_restatement_properties():
     # padding columns (65 -> 68) and padding rows (7 -> 128) of the swizzled buffer are zero
     logical = o.logical_scales(sf, m, k // 16, "128x4")
     assert sf.sum() == logical.sum()
+
+
+def _random_gemm_operands(M, N, K, seed):
+    rng = np.random.default_rng(seed)
+    pad = lambda rows: -(-rows // 128) * 128
+    a = rng.integers(0, 256, size=(M, K // 2), dtype=np.uint8)
+    b = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+    a_sf = rng.integers(0x20, 0x60, size=pad(M) * K // 16, dtype=np.uint8)  # finite, moderate E4M3 codes
+    b_sf = rng.integers(0x20, 0x60, size=pad(N) * K // 16, dtype=np.uint8)
+    return a, b, a_sf, b_sf
+
+
+def test_gemm_oracle_on_sampled_rows_equals_those_rows_of_the_full_product():
+    a, b, a_sf, b_sf = _random_gemm_operands(200, 128, 512, seed=3)
+    full = o.nvfp4_gemm(a, b, a_sf, b_sf, 2.0 ** -9)
+    rows = np.array([0, 7, 31, 32, 127, 128, 199])
+    assert np.array_equal(o.nvfp4_gemm(a, b, a_sf, b_sf, 2.0 ** -9, rows=rows), full[rows])
+
+
+def test_torch_side_gemm_checker_agrees_with_the_oracle():
+    """`_checks.dequantized_matmul_fp32` is what run_test holds the GEMM to at full size; here it runs on
+    the CPU, on the oracle's own operands."""
+    import torch
+
+    from tirx_kernels import _checks
+
+    a, b, a_sf, b_sf = _random_gemm_operands(256, 384, 1024, seed=4)
+    want = o.nvfp4_gemm(a, b, a_sf, b_sf, 2.0 ** -9)
+    got = _checks.dequantized_matmul_fp32(torch.from_numpy(a), torch.from_numpy(b), torch.from_numpy(a_sf),
+                                          torch.from_numpy(b_sf), 2.0 ** -9, row_chunk=100)
+    want_t = torch.from_numpy(want.view(np.int16)).view(torch.bfloat16).float()
+    assert float((got.float() - want_t).norm() / want_t.norm()) <= 2e-4

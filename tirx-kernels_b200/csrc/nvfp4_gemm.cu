@@ -30,9 +30,11 @@
 // (tensor memory released); the host reads the word through b2_nvfp4_gemm_status().
 #include <cuda.h>
 
+#include <atomic>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
+#include <vector>
 
 #include "common.cuh"
 
@@ -42,7 +44,7 @@ namespace {
 constexpr int kBlockM = 128;        // rows of A per CTA (TMEM lanes)
 constexpr int kBlockK = 256;        // fp4 values per stage along K = 128 bytes = one swizzle row
 constexpr int kThreads = 576;       // TMA warp, MMA warp, 2 x 4 scale warps, 8 epilogue warps
-constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;  // one second per wait
+constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;  // default budget of a wait: one second
 
 struct GemmParams {
   const float* alpha;
@@ -57,6 +59,9 @@ struct GemmParams {
   float* partial;    // [splits][M][N] fp32 partial sums when splits > 1
   int tiles_m, tiles_n;  // in units of (cta_group * 128) rows and BN columns
   int group_n;           // tile-order grouping along N
+  uint64_t wait_budget_ns;  // budget of a bounded wait (kWaitBudgetNs unless a test shortened it)
+  int test_fault;        // test hook, 0 in production: 1 = the first slab of CTA 0 announces 16 bytes more
+                         // than its copies deliver, so its barrier never completes (every copy still lands)
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------
@@ -281,14 +286,19 @@ struct SmemLayout {
 struct WaitCtx {
   uint32_t* status;
   volatile uint32_t* abort_flag;  // in shared memory
+  uint64_t budget_ns;
 };
 
 // Bounded mbarrier wait.  Returns false after recording `code` when the barrier never flips or
-// another role of this CTA has already given up.
+// another role of this CTA has already given up.  The waits on data arriving from memory (codes 3
+// and 5) run out after the budget, the waits downstream of them (a free stage, a drained or a
+// finished accumulator) after twice the budget, so that the status word names the role that
+// stalled first rather than one that only waited for it.
 template <bool kClusterAcquire = false>
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
                                               uint32_t code) {
   uint64_t started = 0;
+  const uint64_t budget = (code == 3u || code == 5u) ? ctx.budget_ns : 2 * ctx.budget_ns;
   for (uint32_t i = 0;; ++i) {
     const bool ok = kClusterAcquire ? mbar_try_wait_cluster_acquire(bar, parity) : mbar_try_wait(bar, parity);
     if (ok) return true;
@@ -296,7 +306,7 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, con
     if (*ctx.abort_flag) return false;
     const uint64_t now = globaltimer_ns();
     if (started == 0) started = now;
-    else if (now - started > kWaitBudgetNs) break;
+    else if (now - started > budget) break;
   }
   if (atomicCAS(ctx.status, 0u, code) == 0u) ctx.status[1] = blockIdx.x;
   *ctx.abort_flag = 1u;
@@ -380,7 +390,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem_empty_bar = bar_base + 8u * (3 * STAGES + 1);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + L::kRingBytes + 8 * (3 * STAGES + 2));
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  const WaitCtx ctx{p.status, abort_flag};
+  const WaitCtx ctx{p.status, abort_flag, p.wait_budget_ns};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -427,6 +437,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
+      uint32_t excess_tx = (p.test_fault == 1 && blockIdx.x == 0) ? 16u : 0u;  // test hook, see GemmParams
       long long t_wait = 0, t_begin = prof ? clock64() : 0;
       for (int t = unit; t < num_tiles && alive; t += num_units) {
         int tm, tn;
@@ -441,7 +452,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint32_t sbase = smem_base + stage * L::kStageBytes;
           // operand bytes of both CTAs of a pair are counted on the leader's barrier
           const uint32_t op_bar = CG == 2 ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
-          if (leader) mbar_expect_tx(full_bar(stage), kOperandTx);
+          if (leader) mbar_expect_tx(full_bar(stage), kOperandTx + excess_tx);
+          excess_tx = 0;
           mbar_expect_tx(sfload_bar(stage), kScaleTx);
           tma_load_3d<1>(sbase + L::kABytes + L::kBBytes, &map_sfa, 0, ks * 4, row_a / 128, sfload_bar(stage));
           tma_load_3d<1>(sbase + L::kABytes + L::kBBytes + L::kSfaBytes, &map_sfb, 0, ks * 4, (tn * BN) / 128,
@@ -784,7 +796,9 @@ std::mutex g_mu;
 std::unordered_map<MapKey, MapSet, MapKeyHash> g_maps;
 uint32_t* g_status[64] = {nullptr};
 constexpr int kStatusWords = 64;  // 2 status words, padding, 12 64-bit role timers from word 16
-int g_profile = 0;
+std::atomic<int> g_profile{0};
+std::atomic<unsigned long long> g_wait_budget_ns{kWaitBudgetNs};
+std::atomic<int> g_test_fault{0};  // consumed by the next launch
 
 
 // Device status word of the current device, allocated (and zeroed) on first use.
@@ -878,7 +892,7 @@ int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N
   p.ldd = gather.ldd ? gather.ldd : N;
   p.col0 = gather.col0;
   p.status = status;
-  p.profile = g_profile;
+  p.profile = g_profile.load(std::memory_order_relaxed);
   p.M = M;
   p.N = N;
   p.K = K;
@@ -887,14 +901,23 @@ int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N
   p.tiles_m = (M + kBlockM * CG - 1) / (kBlockM * CG);
   p.tiles_n = N / BN;
   p.group_n = 8;
+  p.wait_budget_ns = g_wait_budget_ns.load(std::memory_order_relaxed);
+  p.test_fault = g_test_fault.exchange(0, std::memory_order_relaxed);
   const int sms = device_sm_count();
   if (sms <= 0) return B2_ERR_CUDA;
   const int units = std::min(p.tiles_m * p.tiles_n * splits, sms / CG);
 
-  static bool configured = false;  // per template instantiation
-  if (!configured) {
-    B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    configured = true;
+  // The shared-memory limit of a kernel is an attribute per device: set it once for every device
+  // ordinal this instantiation is launched on.
+  {
+    static bool configured[64] = {};  // per template instantiation, guarded by g_mu
+    int dev = 0;
+    B2_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+      B2_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+      if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(units * CG);
@@ -932,24 +955,31 @@ int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N
 struct Scratch {
   float* ptr = nullptr;
   size_t bytes = 0;
+  std::vector<void*> retired;  // outgrown buffers: earlier launches and captured graphs may still name them
 };
 Scratch g_scratch[64];
+constexpr size_t kFirstScratchBytes = 32u << 20;  // covers 8 K ranges x 128 x 8192 fp32
 
-// Per-device scratch for split-K partial sums, grown on demand (cudaFree synchronises the device,
-// so a buffer still in use by earlier launches is never released under them).
+// Per-device scratch for split-K partial sums.  The first request allocates 32 MiB (or what the
+// request needs, if more); a larger request later allocates a new buffer and keeps the old one
+// alive until the process exits, so nothing is ever freed under a launch in flight or a captured
+// graph, and the launch path never takes the device-wide synchronisation of cudaFree.
 int partial_scratch(size_t bytes, float** out) {
   int dev = 0;
   B2_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    set_error("device ordinal %d out of range", dev);
+    return B2_ERR_CUDA;
+  }
   std::lock_guard<std::mutex> lock(g_mu);
-  Scratch& sc = g_scratch[dev & 63];
+  Scratch& sc = g_scratch[dev];
   if (sc.bytes < bytes) {
-    if (sc.ptr) B2_CUDA_TRY(cudaFree(sc.ptr));
-    sc.ptr = nullptr;
-    sc.bytes = 0;
+    const size_t want = bytes > kFirstScratchBytes ? bytes : kFirstScratchBytes;
     void* fresh = nullptr;
-    B2_CUDA_TRY(cudaMalloc(&fresh, bytes));
+    B2_CUDA_TRY(cudaMalloc(&fresh, want));
+    if (sc.ptr) sc.retired.push_back(sc.ptr);
     sc.ptr = static_cast<float*>(fresh);
-    sc.bytes = bytes;
+    sc.bytes = want;
   }
   *out = sc.ptr;
   return B2_OK;
@@ -966,11 +996,40 @@ int choose_splits(int tiles, int k_slabs, int units_available) {
   return splits;
 }
 
+// Status words and split-K scratch a caller-independent source provides (the array built into the
+// library, for the entry point that must not allocate); null = the library's allocated ones.
+struct FixedWorkspace {
+  uint32_t* status;
+  float* partial;
+  size_t partial_bytes;
+  const char* who;
+};
+
 template <int CG, int BN, int STAGES, int TMA_OUT = 0, int AM = kBlockM>
 int launch_variant(const void* A, const void* B, const void* SFA, const void* SFB, const float* alpha,
-                   void* D, int M, int N, int K, int variant, cudaStream_t stream) {
+                   void* D, int M, int N, int K, int variant, cudaStream_t stream,
+                   const FixedWorkspace* fixed = nullptr) {
+  const int sms = device_sm_count();
+  if (sms <= 0) return B2_ERR_CUDA;
+  const int tiles = ((M + kBlockM * CG - 1) / (kBlockM * CG)) * (N / BN);
+  const int splits = choose_splits(tiles, K / kBlockK, sms / CG);
+  const size_t need = splits > 1 ? static_cast<size_t>(splits) * M * N * sizeof(float) : 0;
   uint32_t* status = nullptr;
-  if (int rc = status_word(&status)) return rc;
+  float* partial = nullptr;
+  if (fixed) {
+    if (need > fixed->partial_bytes) {
+      set_error("%s: M=%d N=%d K=%d needs %zu bytes of partial sums (%d K ranges), the built-in scratch holds "
+                "%zu; use b2_nvfp4_gemm", fixed->who, M, N, K, need, splits, fixed->partial_bytes);
+      return B2_ERR_INVALID_ARGUMENT;
+    }
+    status = fixed->status;
+    partial = fixed->partial;
+  } else {
+    if (int rc = status_word(&status)) return rc;
+    if (need) {
+      if (int rc = partial_scratch(need, &partial)) return rc;
+    }
+  }
   MapSet maps;
   {
     const MapKey key{A, B, SFA, SFB, M, N, K, variant};
@@ -984,14 +1043,6 @@ int launch_variant(const void* A, const void* B, const void* SFA, const void* SF
     }
     maps = it->second;
   }
-  const int sms = device_sm_count();
-  if (sms <= 0) return B2_ERR_CUDA;
-  const int tiles = ((M + kBlockM * CG - 1) / (kBlockM * CG)) * (N / BN);
-  const int splits = choose_splits(tiles, K / kBlockK, sms / CG);
-  float* partial = nullptr;
-  if (splits > 1) {
-    if (int rc = partial_scratch(static_cast<size_t>(splits) * M * N * sizeof(float), &partial)) return rc;
-  }
   if constexpr (TMA_OUT > 0) {
     OutMaps<true> out_maps;
     {
@@ -1001,6 +1052,7 @@ int launch_variant(const void* A, const void* B, const void* SFA, const void* SF
       if (it == g_maps.end()) {
         MapSet fresh;
         if (int rc = encode_output_map(&fresh.a, D, M, N)) return rc;
+        if (g_maps.size() > 4096) g_maps.clear();
         it = g_maps.emplace(key, fresh).first;
       }
       out_maps.m[0] = it->second.a;
@@ -1014,7 +1066,36 @@ int launch_variant(const void* A, const void* B, const void* SFA, const void* SF
   }
 }
 
-int g_forced_variant = -1;  // test hook: -1 = automatic
+std::atomic<int> g_forced_variant{-1};  // test hook: -1 = automatic
+
+// Automatic choice of the kernel variant (numbering of b2_nvfp4_gemm_set_variant).
+int choose_variant(int M, int N, int K) {
+  const int sms = device_sm_count();
+  if (M <= 128) {
+    // Decode-sized M: single-CTA tiles and K ranges to fill the GPU.  The time goes with the slabs
+    // one CTA runs in series (waves x slabs per work item); a 256-wide slab costs about 1.8 of a
+    // 128-wide one, and its four-fold partial sums only pay off while M is small.
+    int variant = 0;
+    if (sms > 0 && M <= 32 && N % 256 == 0) {
+      const int k_slabs = K / kBlockK;
+      auto serial_slabs = [&](int bn) {
+        const int tiles = N / bn;
+        const int splits = choose_splits(tiles, k_slabs, sms);
+        return static_cast<double>((tiles * splits + sms - 1) / sms) * (k_slabs / splits);
+      };
+      if (1.8 * serial_slabs(256) < serial_slabs(128)) variant = 1;
+    }
+    if (M <= 32) variant += 4;  // 32 rows of A per stage, deeper ring
+    return variant;
+  }
+  int variant = N % 256 == 0 ? 2 : 3;
+  if (variant == 2) {
+    // few 256 x 256 tiles (fewer than half the CTA pairs busy): 256 x 128 tiles double the parallelism
+    const int64_t tiles = static_cast<int64_t>((M + 255) / 256) * (N / 256);
+    if (sms > 0 && tiles * 2 <= sms / 2) variant = 3;
+  }
+  return variant;
+}
 
 }  // namespace
 }  // namespace b2
@@ -1028,7 +1109,7 @@ extern "C" int b2_nvfp4_gemm_set_variant(int variant) {
     b2::set_error("b2_nvfp4_gemm_set_variant: unknown variant %d", variant);
     return B2_ERR_INVALID_ARGUMENT;
   }
-  b2::g_forced_variant = variant;
+  b2::g_forced_variant.store(variant, std::memory_order_relaxed);
   return B2_OK;
 }
 
@@ -1055,34 +1136,8 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
     return B2_ERR_CUDA;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int variant = g_forced_variant;
-  if (variant < 0) {
-    const bool pair_ok = M > 128;
-    if (!pair_ok) {
-      // Decode-sized M: single-CTA tiles and K ranges to fill the GPU.  The time goes with the slabs
-      // one CTA runs in series (waves x slabs per work item); a 256-wide slab costs about 1.8 of a
-      // 128-wide one, and its four-fold partial sums only pay off while M is small.
-      variant = 0;
-      const int sms = device_sm_count();
-      if (sms > 0 && M <= 32 && N % 256 == 0) {
-        const int k_slabs = K / kBlockK;
-        auto serial_slabs = [&](int bn) {
-          const int tiles = N / bn;
-          const int splits = choose_splits(tiles, k_slabs, sms);
-          return static_cast<double>((tiles * splits + sms - 1) / sms) * (k_slabs / splits);
-        };
-        if (1.8 * serial_slabs(256) < serial_slabs(128)) variant = 1;
-      }
-      if (M <= 32) variant += 4;  // 32 rows of A per stage, deeper ring
-    }
-    else variant = N % 256 == 0 ? 2 : 3;
-    if (variant == 2) {
-      // few 256 x 256 tiles (fewer than half the CTA pairs busy): 256 x 128 tiles double the parallelism
-      const int sms = device_sm_count();
-      const int64_t tiles = static_cast<int64_t>((M + 255) / 256) * (N / 256);
-      if (sms > 0 && tiles * 2 <= sms / 2) variant = 3;
-    }
-  }
+  int variant = g_forced_variant.load(std::memory_order_relaxed);
+  if (variant < 0) variant = choose_variant(M, N, K);
   if ((variant == 4 || variant == 5) && M > 32) {
     set_error("b2_nvfp4_gemm: variant %d needs M <= 32", variant);
     return B2_ERR_INVALID_ARGUMENT;
@@ -1109,7 +1164,7 @@ extern "C" int b2_nvfp4_gemm_role_timers(int enable, unsigned long long* out12, 
   using namespace b2;
   uint32_t* status = nullptr;
   if (int rc = status_word(&status)) return rc;
-  g_profile = enable ? 1 : 0;
+  g_profile.store(enable ? 1 : 0, std::memory_order_relaxed);
   if (out12) {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     B2_CUDA_TRY(cudaMemcpyAsync(out12, status + 16, 12 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s));
@@ -1118,12 +1173,11 @@ extern "C" int b2_nvfp4_gemm_role_timers(int enable, unsigned long long* out12, 
   return B2_OK;
 }
 
-extern "C" int b2_nvfp4_gemm_status(void* stream) {
-  using namespace b2;
-  uint32_t* status = nullptr;
-  if (int rc = status_word(&status)) return rc;
+namespace b2 {
+namespace {
+// Reads and clears the two status words at `status`; `who` prefixes the message.
+int read_status(uint32_t* status, const char* who, cudaStream_t s) {
   uint32_t host[2] = {0, 0};
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
   B2_CUDA_TRY(cudaMemcpyAsync(host, status, sizeof(host), cudaMemcpyDeviceToHost, s));
   B2_CUDA_TRY(cudaStreamSynchronize(s));
   if (host[0] == 0) return B2_OK;
@@ -1135,9 +1189,17 @@ extern "C" int b2_nvfp4_gemm_status(void* stream) {
                                       "epilogue waiting for the accumulator",
                                       "scale warp waiting for loaded scale factors",
                                       "(unused)"};
-  set_error("b2_nvfp4_gemm: bounded wait expired (%s) in CTA %u", host[0] < 7 ? kWhat[host[0]] : "unknown",
-            host[1]);
+  set_error("%s: bounded wait expired (%s) in CTA %u", who, host[0] < 7 ? kWhat[host[0]] : "unknown", host[1]);
   return B2_ERR_DEVICE_TIMEOUT;
+}
+}  // namespace
+}  // namespace b2
+
+extern "C" int b2_nvfp4_gemm_status(void* stream) {
+  using namespace b2;
+  uint32_t* status = nullptr;
+  if (int rc = status_word(&status)) return rc;
+  return read_status(status, "b2_nvfp4_gemm", static_cast<cudaStream_t>(stream));
 }
 
 // ---- decode-sized GEMM for callers that must not allocate ---------------------------------------
@@ -1183,22 +1245,22 @@ int builtin_scratch(unsigned char** out) {
 }  // namespace
 }  // namespace b2
 
-// D[M,N] (bf16) = alpha * A[M,K] * B[N,K]^T for M <= 128, same operands and result as
-// b2_nvfp4_gemm, without any device allocation: no cudaMalloc, cudaFree or allocating library
-// routine is called, here or on first use.  The split-K partial sums and the kernel's status
-// words live in an array built into the library (4 MiB + 256 B per GPU that loads it).
+// D[M,N] (bf16) = alpha * A[M,K] * B[N,K]^T for M <= 128: the operands, the kernel variant, the K
+// ranges and therefore the bits of the result are those of b2_nvfp4_gemm, without any device
+// allocation: no cudaMalloc, cudaFree or allocating library routine is called, here or on first
+// use.  The split-K partial sums and the kernel's status words live in an array built into the
+// library (4 MiB + 256 B per GPU that loads it).
 //
 //  * The first call on a device looks the array's device address up (cudaGetSymbolAddress) and
 //    sets the kernel's shared-memory attribute; make that first call before any stream capture.
-//  * A problem whose partial sums (K ranges x M x N x 4 bytes, the ranges chosen as in
-//    b2_nvfp4_gemm) exceed 4 MiB is rejected with B2_ERR_INVALID_ARGUMENT and nothing is launched.
+//  * A problem whose partial sums (K ranges x M x N x 4 bytes) exceed 4 MiB is rejected with
+//    B2_ERR_INVALID_ARGUMENT and nothing is launched.
 //  * Every call on a device uses the same array, which keeps the previous call's contents.  Each
 //    call overwrites all partial sums it later reads, so nothing needs clearing, but two calls
 //    that overlap on the GPU (different streams, or graphs replayed concurrently) race on it:
 //    keep calls of this entry point on one device in stream order.
-//  * Tensor maps are encoded on every call instead of being cached.  A bounded wait that expires
-//    still ends the kernel cleanly, but its code is written to the built-in status words, which
-//    b2_nvfp4_gemm_status does not read.
+//  * A bounded wait that expires still ends the kernel cleanly; its code goes to the built-in
+//    status words, which b2_nvfp4_gemm_small_m_noalloc_status reads and clears.
 extern "C" int b2_nvfp4_gemm_small_m_noalloc(const void* A, const void* B, const void* SFA, const void* SFB,
                                              const float* alpha_dev, void* D, int M, int N, int K,
                                              void* stream) {
@@ -1223,22 +1285,53 @@ extern "C" int b2_nvfp4_gemm_small_m_noalloc(const void* A, const void* B, const
     set_error("b2_nvfp4_gemm_small_m_noalloc: cuTensorMapEncodeTiled is not available from this driver");
     return B2_ERR_CUDA;
   }
-  const int sms = device_sm_count();
-  if (sms <= 0) return B2_ERR_CUDA;
-  const int splits = choose_splits(N / 128, K / kBlockK, sms);
-  const size_t need = splits > 1 ? static_cast<size_t>(splits) * M * N * sizeof(float) : 0;
-  if (need > kBuiltinPartialBytes) {
-    set_error("b2_nvfp4_gemm_small_m_noalloc: M=%d N=%d needs %zu bytes of partial sums, the built-in scratch "
-              "holds %zu; use b2_nvfp4_gemm", M, N, need, kBuiltinPartialBytes);
-    return B2_ERR_INVALID_ARGUMENT;
-  }
   unsigned char* base = nullptr;
   if (int rc = builtin_scratch(&base)) return rc;
-  MapSet maps;
-  if (int rc = encode_maps<1, 128, 6>(&maps, A, B, SFA, SFB, M, N, K)) return rc;
-  return launch_kernels<1, 128, 6>(maps, alpha_dev, D, M, N, K, splits,
-                                   reinterpret_cast<uint32_t*>(base + kBuiltinPartialBytes),
-                                   reinterpret_cast<float*>(base), static_cast<cudaStream_t>(stream));
+  const FixedWorkspace ws{reinterpret_cast<uint32_t*>(base + kBuiltinPartialBytes), reinterpret_cast<float*>(base),
+                          kBuiltinPartialBytes, "b2_nvfp4_gemm_small_m_noalloc"};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (choose_variant(M, N, K)) {
+    case 0: return launch_variant<1, 128, 6>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 0, s, &ws);
+    case 1: return launch_variant<1, 256, 4>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 1, s, &ws);
+    case 4: return launch_variant<1, 128, 9, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 4, s, &ws);
+    default: return launch_variant<1, 256, 5, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 5, s, &ws);
+  }
+}
+
+// Status of the launches of b2_nvfp4_gemm_small_m_noalloc on the current device: synchronises
+// `stream`, returns B2_OK or B2_ERR_DEVICE_TIMEOUT (detail in b2_last_error()) and clears the
+// words.  Allocates nothing: an 8-byte copy out of the built-in array and, after a failure, an
+// 8-byte memset.
+extern "C" int b2_nvfp4_gemm_small_m_noalloc_status(void* stream) {
+  using namespace b2;
+  unsigned char* base = nullptr;
+  if (int rc = builtin_scratch(&base)) return rc;
+  return read_status(reinterpret_cast<uint32_t*>(base + kBuiltinPartialBytes), "b2_nvfp4_gemm_small_m_noalloc",
+                     static_cast<cudaStream_t>(stream));
+}
+
+// Test hooks of the bounded waits.  `milliseconds` > 0 shortens the budget of every device-side
+// wait of later launches (0 restores the one-second default).  `fault` = 1 makes the NEXT launch
+// announce, for the first K slab of CTA 0, 16 bytes more than its copies deliver: every copy lands,
+// nothing stays in flight, the slab's barrier simply never completes, the MMA role's wait runs out
+// and the kernel ends through its abort path.  Both are off unless a test turns them on.
+extern "C" int b2_nvfp4_gemm_set_wait_budget_ms(int milliseconds) {
+  if (milliseconds < 0 || milliseconds > 10000) {
+    b2::set_error("b2_nvfp4_gemm_set_wait_budget_ms: %d ms out of range [0, 10000]", milliseconds);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  b2::g_wait_budget_ns.store(milliseconds ? 1000000ull * static_cast<unsigned long long>(milliseconds) : b2::kWaitBudgetNs,
+                             std::memory_order_relaxed);
+  return B2_OK;
+}
+
+extern "C" int b2_nvfp4_gemm_inject_test_fault(int fault) {
+  if (fault < 0 || fault > 1) {
+    b2::set_error("b2_nvfp4_gemm_inject_test_fault: unknown fault %d", fault);
+    return B2_ERR_INVALID_ARGUMENT;
+  }
+  b2::g_test_fault.store(fault, std::memory_order_relaxed);
+  return B2_OK;
 }
 
 // ---- sharded projection: GEMM with the output all-gather fused into its epilogue ---------------

@@ -75,6 +75,36 @@ def dequantize(packed, sf, layout: str, *, block_size: int = 16, scale_format: s
     return (values.view(m, -1, block_size) * scales[..., None]).reshape(m, k)
 
 
+def dequantized_matmul_fp32(A_fp4, B_fp4, A_sf, B_sf, alpha: float, *, row_chunk: int = 2048):
+    """bf16 [M, N] of alpha * dequantize(A) @ dequantize(B)^T in fp32 with TF32 off, on the device of
+    the operands: the checker the GEMM is held to at sizes a CPU oracle cannot afford in full.  A is
+    decoded in row chunks so that the temporaries stay small beside the operands."""
+    import torch
+
+    M, N = A_fp4.shape[0], B_fp4.shape[0]
+    k = A_fp4.shape[1] * 2
+    tf32 = torch.backends.cuda.matmul.allow_tf32
+    precision = torch.get_float32_matmul_precision()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.set_float32_matmul_precision("highest")
+    try:
+        b = torch.empty(N, k, dtype=torch.float32, device=B_fp4.device)
+        sf_b = logical_scale_bytes(B_sf, N, k // 16, "128x4").view(torch.float8_e4m3fn)
+        for r0 in range(0, N, row_chunk):
+            r1 = min(N, r0 + row_chunk)
+            b[r0:r1] = (unpack_e2m1(B_fp4[r0:r1]).view(r1 - r0, -1, 16) * sf_b[r0:r1].float()[..., None]).reshape(r1 - r0, k)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=A_fp4.device)
+        sf_a = logical_scale_bytes(A_sf, M, k // 16, "128x4").view(torch.float8_e4m3fn)
+        for r0 in range(0, M, row_chunk):
+            r1 = min(M, r0 + row_chunk)
+            a = (unpack_e2m1(A_fp4[r0:r1]).view(r1 - r0, -1, 16) * sf_a[r0:r1].float()[..., None]).reshape(r1 - r0, k)
+            out[r0:r1] = (torch.mm(a, b.t()) * float(alpha)).to(torch.bfloat16)
+        return out
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+        torch.set_float32_matmul_precision(precision)
+
+
 def padding_mask(m: int, sf_cols: int, layout: str, device):
     """bool mask over a swizzled buffer: True where no logical (row < m, col < sf_cols) scale lives."""
     import torch

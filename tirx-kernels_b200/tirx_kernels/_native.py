@@ -37,6 +37,9 @@ MAIN_SIGNATURES = {
     "b2_nvfp4_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "b2_nvfp4_gemm_small_m_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "b2_nvfp4_gemm_status": (_i, [_vp]),
+    "b2_nvfp4_gemm_small_m_noalloc_status": (_i, [_vp]),
+    "b2_nvfp4_gemm_set_wait_budget_ms": (_i, [_i]),
+    "b2_nvfp4_gemm_inject_test_fault": (_i, [_i]),
     "b2_nvfp4_gemm_set_variant": (_i, [_i]),
     "b2_nvfp4_gemm_role_timers": (_i, [_i, _vp, _vp]),
     "b2_mufu_probe": (_i, [_i, _vp, _vp, _i, _vp]),
@@ -262,6 +265,20 @@ def nvfp4_gemm_set_variant(variant: int) -> None:
 
 def nvfp4_gemm_status() -> None:
     check(lib().b2_nvfp4_gemm_status(current_stream_ptr()), "b2_nvfp4_gemm_status")
+
+
+def nvfp4_gemm_small_m_noalloc_status() -> None:
+    check(lib().b2_nvfp4_gemm_small_m_noalloc_status(current_stream_ptr()), "b2_nvfp4_gemm_small_m_noalloc_status")
+
+
+def nvfp4_gemm_set_wait_budget_ms(milliseconds: int) -> None:
+    """Test hook: budget of the kernels' bounded waits (0 = the default, one second)."""
+    check(lib().b2_nvfp4_gemm_set_wait_budget_ms(int(milliseconds)), "b2_nvfp4_gemm_set_wait_budget_ms")
+
+
+def nvfp4_gemm_inject_test_fault(fault: int) -> None:
+    """Test hook: 1 = the next launch's first K slab never completes its barrier (no fault, no hang)."""
+    check(lib().b2_nvfp4_gemm_inject_test_fault(int(fault)), "b2_nvfp4_gemm_inject_test_fault")
 
 
 def nvfp4_gemm_cublaslt(A, B, SFA, SFB, alpha: float, D, M: int, N: int, K: int) -> None:
