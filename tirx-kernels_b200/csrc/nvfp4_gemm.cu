@@ -43,7 +43,16 @@ namespace {
 
 constexpr int kBlockM = 128;        // rows of A per CTA (TMEM lanes)
 constexpr int kBlockK = 256;        // fp4 values per stage along K = 128 bytes = one swizzle row
-constexpr int kThreads = 576;       // TMA warp, MMA warp, 2 x 4 scale warps, 8 epilogue warps
+constexpr int kThreads = 608;       // operand TMA warp, MMA warp, 2 x 4 scale warps, 8 epilogue warps, scale TMA warp
+// The MMA role's waits on barriers that the peer CTA of a pair arrives on.  What those arrivals publish
+// lives in tensor memory or was written by the TMA, none of it is read through the generic proxy by the
+// waiting thread, and tcgen05.fence::after_thread_sync follows every wait, so the default (CTA-scope)
+// acquire of mbarrier.try_wait is what the wait needs; the cluster-scope form costs the issuing thread
+// on the order of a hundred cycles per K slab.
+#ifndef B2_GEMM_CLUSTER_ACQUIRE
+#define B2_GEMM_CLUSTER_ACQUIRE 0
+#endif
+constexpr bool kClusterAcquireWaits = B2_GEMM_CLUSTER_ACQUIRE != 0;
 constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;  // default budget of a wait: one second
 
 struct GemmParams {
@@ -263,7 +272,6 @@ struct SmemLayout {
   static constexpr int kBRows = BN / CG;                       // rows of B held by one CTA
   static constexpr int kChunks = BN / 128 > 0 ? BN / 128 : 1;  // 128-row scale chunks of B
   static constexpr int kABytes = AM * 128;
-  static_assert(AM == kBlockM || (CG == 1 && kABytes + BN * 128 >= kBlockM * 128), "the MMA's 128-row window stays inside the stage");
   static constexpr int kBBytes = kBRows * 128;
   static constexpr int kSfaBytes = 4 * 512;                    // 4 K-blocks of 64, 512 B each
   static constexpr int kSfbBytes = kChunks * 4 * 512;
@@ -278,6 +286,7 @@ struct SmemLayout {
   static constexpr int kRingBytes = STAGES * kStageBytes + kStagingBytes;
   static constexpr int kTotal = kRingBytes + kBarrierBytes + 1024;  // + alignment slack
   static_assert(kStageBytes % 1024 == 0, "stages and staging stay 1024-byte aligned");
+  static_assert(AM == kBlockM || (CG == 1 && kStageBytes >= kBlockM * 128), "the MMA's 128-row window stays inside the stage");
   static_assert(kTotal <= 227 * 1024, "shared memory budget");
   static_assert(BN + STAGES * kSfCols <= 512, "tensor memory budget");
   static_assert((3 * STAGES + 2) * 8 + 16 <= kBarrierBytes, "barrier area");
@@ -341,7 +350,7 @@ __device__ __forceinline__ void tmem_st_wait() {
 
 // Warp roles.  The scale and epilogue warps are placed so that (warp & 3) is the 32-lane quarter of
 // tensor memory the warp is allowed to touch.
-constexpr int kWarpProducer = 0, kWarpMma = 1, kWarpScale0 = 2, kWarpEpi0 = 10;
+constexpr int kWarpProducer = 0, kWarpMma = 1, kWarpScale0 = 2, kWarpEpi0 = 10, kWarpScaleProducer = 18;
 
 // Output tensor maps of the TMA-store epilogue: [0] this GPU's buffer, [1..] the peers' buffers.
 template <bool TMA_OUT>
@@ -351,9 +360,16 @@ struct OutMaps<true> {
   CUtensorMap m[8];
 };
 
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x),
-               "r"(y), "r"(smem)
+// The output is written once and not read again by this kernel: its lines are marked evict-first so
+// that they do not push the operands, which every tile row and column re-reads, out of L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem, int x, int y, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%1, %2}], [%3], %4;" ::"l"(map),
+               "r"(x), "r"(y), "r"(smem), "l"(policy)
                : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
@@ -454,10 +470,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint32_t op_bar = CG == 2 ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
           if (leader) mbar_expect_tx(full_bar(stage), kOperandTx + excess_tx);
           excess_tx = 0;
-          mbar_expect_tx(sfload_bar(stage), kScaleTx);
-          tma_load_3d<1>(sbase + L::kABytes + L::kBBytes, &map_sfa, 0, ks * 4, row_a / 128, sfload_bar(stage));
-          tma_load_3d<1>(sbase + L::kABytes + L::kBBytes + L::kSfaBytes, &map_sfb, 0, ks * 4, (tn * BN) / 128,
-                         sfload_bar(stage));
           tma_load_2d<CG>(sbase, &map_a, ks * 128, row_a, op_bar);
           tma_load_2d<CG>(sbase + L::kABytes, &map_b, ks * 128, row_b, op_bar);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -478,12 +490,20 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint64_t ns_begin = prof ? globaltimer_ns() : 0;
       for (int t = unit; t < num_tiles && alive; t += num_units) {
         const long long a0 = prof ? clock64() : 0;
-        if (!wait_or_abort<CG == 2>(tmem_empty_bar, acc_phase ^ 1u, ctx, 2u)) break;
+        if (!wait_or_abort<kClusterAcquireWaits && CG == 2>(tmem_empty_bar, acc_phase ^ 1u, ctx, 2u)) break;
         if (prof) t_acc += clock64() - a0;
         tc_fence_after();
+        // A 64-wide tile uses half of a 128-row scale chunk of B: the MMA reads N / 32 scale columns from
+        // the address it is given, so the upper half starts two columns in.
+        uint32_t sfb_half = 0;
+        if constexpr (BN == 64) {
+          int tm, tn;
+          tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
+          sfb_half = static_cast<uint32_t>(tn & 1) * 2u;
+        }
         for (int ks = 0; ks < k_slabs; ++ks) {
           const long long w0 = prof ? clock64() : 0;
-          if (!wait_or_abort<CG == 2>(full_bar(stage), phase, ctx, 3u)) { alive = false; break; }
+          if (!wait_or_abort<kClusterAcquireWaits && CG == 2>(full_bar(stage), phase, ctx, 3u)) { alive = false; break; }
           const long long w1 = prof ? clock64() : 0;
           t_full += w1 - w0;
           tc_fence_after();
@@ -495,7 +515,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int kb = 0; kb < 4; ++kb) {
             // 64 fp4 values = 32 bytes = 2 descriptor address units inside the swizzled row
             tc_mma<CG>(tmem_base, a_desc + 2 * kb, b_desc + 2 * kb, kIdesc, sf_tmem + kb * 4,
-                       sf_tmem + 16 + kb * 4 * L::kChunks, (ks | kb) ? 1u : 0u);
+                       sf_tmem + 16 + kb * 4 * L::kChunks + sfb_half, (ks | kb) ? 1u : 0u);
           }
           if constexpr (CG == 2) tc_commit_pair(empty_bar(stage));
           else tc_commit<CG>(empty_bar(stage));
@@ -564,12 +584,36 @@ __global__ void __launch_bounds__(kThreads, 1)
       counters[9] = t_wait;
       counters[10] = t_body;
     }
+  } else if (warp == kWarpScaleProducer) {
+    // ================= TMA producer of the scale factors =================
+    // A thread of its own: issuing a TMA copy costs its thread on the order of a hundred cycles, and
+    // four of them in one thread per slab made that thread the slowest stage of the pipeline.
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int t = unit; t < num_tiles && alive; t += num_units) {
+        int tm, tn;
+        tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
+        const int row_a = (tm * CG + static_cast<int>(rank)) * kBlockM;
+        const int k_first = (t % p.splits) * k_slabs;
+        for (int ks = k_first; ks < k_first + k_slabs; ++ks) {
+          if (!wait_or_abort(empty_bar(stage), phase ^ 1u, ctx, 1u)) { alive = false; break; }
+          const uint32_t sf_smem = smem_base + stage * L::kStageBytes + L::kABytes + L::kBBytes;
+          mbar_expect_tx(sfload_bar(stage), kScaleTx);
+          tma_load_3d<1>(sf_smem, &map_sfa, 0, ks * 4, row_a / 128, sfload_bar(stage));
+          tma_load_3d<1>(sf_smem + L::kSfaBytes, &map_sfb, 0, ks * 4, (tn * BN) / 128, sfload_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
   } else {
     // ================= epilogue: 8 warps, lane quarter = warp & 3, column half = (warp - 10) / 4 ===========
     constexpr int kHalf = BN / 2;
     const int quarter = warp & 3;
     const int half = (warp - kWarpEpi0) >> 2;
     const float alpha = __ldg(p.alpha);
+    const uint64_t store_policy = l2_policy_evict_first();
     uint32_t acc_phase = 0;
     const uint32_t empty_target = CG == 2 ? mapa_shared(tmem_empty_bar, 0) : tmem_empty_bar;
     const bool eprof = prof && warp == kWarpEpi0;
@@ -590,17 +634,20 @@ __global__ void __launch_bounds__(kThreads, 1)
       // the stores.
       if (p.splits > 1) {
         // split K: this work item's fp32 partial sums go to scratch; a second kernel adds the ranges
-        float* prow = p.partial + (static_cast<int64_t>(t % p.splits) * p.M + row) * p.N +
-                      static_cast<int64_t>(tn) * BN + half * kHalf;
+        if ((tm * CG + static_cast<int>(rank)) * kBlockM + quarter * 32 < p.M) {
+          // (a decode-sized M leaves most lane quarters without a single row to drain)
+          float* prow = p.partial + (static_cast<int64_t>(t % p.splits) * p.M + row) * p.N +
+                        static_cast<int64_t>(tn) * BN + half * kHalf;
 #pragma unroll 1
-        for (int c0 = 0; c0 < kHalf; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * kHalf + c0, v);
-          tmem_ld_wait();
-          if (row < p.M) {
-            uint4* dst = reinterpret_cast<uint4*>(prow + c0);
+          for (int c0 = 0; c0 < kHalf; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * kHalf + c0, v);
+            tmem_ld_wait();
+            if (row < p.M) {
+              uint4* dst = reinterpret_cast<uint4*>(prow + c0);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+              for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            }
           }
         }
         tc_fence_before();
@@ -658,7 +705,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           __syncwarp();
           if (lane == 0) {
             if (row0 < p.M)
-              for (int d = 0; d < p.n_dest; ++d) tma_store_2d(&out_maps.m[d], buf, x0 + sub * 64, row0);
+              for (int d = 0; d < p.n_dest; ++d) tma_store_2d(&out_maps.m[d], buf, x0 + sub * 64, row0, store_policy);
             bulk_commit();
           }
         }
@@ -905,7 +952,12 @@ int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N
   p.test_fault = g_test_fault.exchange(0, std::memory_order_relaxed);
   const int sms = device_sm_count();
   if (sms <= 0) return B2_ERR_CUDA;
-  const int units = std::min(p.tiles_m * p.tiles_n * splits, sms / CG);
+  // Persistent CTAs (pairs): as many as finish the work in the fewest rounds, and no more.  256 tiles on
+  // 74 pairs take four rounds whether 74 or 64 pairs run them; with 64 every round is full and ten pairs
+  // fewer compete for L2 and for the power budget.
+  const int work = p.tiles_m * p.tiles_n * splits;
+  const int rounds = (work + sms / CG - 1) / (sms / CG);
+  const int units = (work + rounds - 1) / rounds;
 
   // The shared-memory limit of a kernel is an attribute per device: set it once for every device
   // ordinal this instantiation is launched on.
@@ -924,14 +976,14 @@ int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = L::kTotal;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  cfg.attrs = attr;
   if (CG == 2) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[cfg.numAttrs].id = cudaLaunchAttributeClusterDimension;
+    attr[cfg.numAttrs].val.clusterDim.x = 2;
+    attr[cfg.numAttrs].val.clusterDim.y = 1;
+    attr[cfg.numAttrs].val.clusterDim.z = 1;
+    ++cfg.numAttrs;
   }
   B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps.a, maps.b, maps.sfa, maps.sfb, p, out_maps));
   if (splits > 1) {
@@ -1105,7 +1157,7 @@ int choose_variant(int M, int N, int K) {
 // 3: CTA pair, N tile 128; 4 and 5: 0 and 1 for M <= 32, loading 32 rows of A per stage into a deeper
 // ring.  Used by the tests to exercise every variant on small shapes.
 extern "C" int b2_nvfp4_gemm_set_variant(int variant) {
-  if (variant < -1 || variant > 5) {
+  if (variant < -1 || variant > 6) {
     b2::set_error("b2_nvfp4_gemm_set_variant: unknown variant %d", variant);
     return B2_ERR_INVALID_ARGUMENT;
   }
@@ -1138,7 +1190,7 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int variant = g_forced_variant.load(std::memory_order_relaxed);
   if (variant < 0) variant = choose_variant(M, N, K);
-  if ((variant == 4 || variant == 5) && M > 32) {
+  if ((variant == 4 || variant == 5 || variant == 6) && M > 32) {
     set_error("b2_nvfp4_gemm: variant %d needs M <= 32", variant);
     return B2_ERR_INVALID_ARGUMENT;
   }
@@ -1152,6 +1204,7 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
     case 2: return launch_variant<2, 256, 5, 1>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 2, s);
     case 4: return launch_variant<1, 128, 9, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 4, s);
     case 5: return launch_variant<1, 256, 5, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 5, s);
+    case 6: return launch_variant<1, 64, 13, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 6, s);
     default: return launch_variant<2, 128, 6, 1>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
   }
 }
