@@ -110,6 +110,15 @@ int b2_rmsnorm_fp4quant(const void* x, const void* w, void* y, void* sf, const f
                         int swizzled, int enable_pdl, void* stream);
 
 /*
+ * Per-CTA timeline of b2_rmsnorm_fp4quant (observability, no counterpart in the reference).  While
+ * `device_buf` is non-null, launches that take the register-resident kernel (rows of up to 16 chunks
+ * per thread, the case of every benchmarked shape) record four 64-bit words per CTA at
+ * device_buf[4 * cta]: start, row sums reduced, end (nanoseconds of the GPU's global timer) and the
+ * SM id.  The buffer needs 4 * ceil(M / rows per CTA) words; 4 * M always suffices.  Null stops it.
+ */
+int b2_rmsnorm_fp4quant_timeline(unsigned long long* device_buf);
+
+/*
  * Residual add + RMSNorm + FP4 block quantization: the executable of
  * tirx_kernels/flashinfer/norm/add_rmsnorm_fp4quant.py:1210-1221 (ABI x, residual, weight, y, scale,
  * scale_unswizzled, y_norm, global_scale, M, eps), called by _launch_tirx :1457-1470; the compile-time

@@ -14,6 +14,7 @@
 // (bit-identical here, the squares being exact in fp32) and the scaling multiplies
 // use the two-wide mul.f32x2.
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -41,7 +42,18 @@ struct RmsParams {
   float inv_h;       // 1.0f / H (exact when pow2)
   int enable_pdl;
   int prefetch_ctas;  // block-owner kernel: look-ahead distance in CTAs (0 = no prefetch)
+  int stagger_ns;     // block-owner kernel: start offset between the CTAs that share an SM at launch (0 = none)
+  int first_ctas;     // CTAs resident at launch (they are the ones that get an offset)
+  int sm_count;
+  int stagger_free;   // CTAs per SM that start at once
+  unsigned long long* timeline;  // block-owner kernel: per CTA {start, rows reduced, end} in ns and the SM id; null = off
 };
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 // acc + x*x for eight values in element order.  The square of a bf16/fp16 value is exact in fp32,
 // so one FMA per element rounds exactly like the reference's mul.f32 followed by add.f32.
@@ -318,7 +330,22 @@ __global__ void __launch_bounds__(128) rmsnorm_fp4quant_block_kernel(const __gri
   const bool row_valid = row < p.M;
   const int lane = tid & 31;
 
+  if (p.timeline && tid == 0) {
+    unsigned int sm;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    p.timeline[blockIdx.x * 4 + 0] = global_timer_ns();
+    p.timeline[blockIdx.x * 4 + 3] = sm;
+  }
   if (p.enable_pdl) pdl_wait();
+  // The CTAs that become resident at launch would all load for the same few microseconds and then all
+  // compute, with HBM idle meanwhile.  Later CTAs start whenever an earlier one leaves and are spread out
+  // by themselves; the first ones are spread out here: the k-th CTA of an SM starts k * stagger_ns late.
+  if (p.stagger_ns > 0 && static_cast<int>(blockIdx.x) < p.first_ctas) {
+    const int slot = static_cast<int>(blockIdx.x) / p.sm_count;
+    const unsigned long long wait_ns = slot < p.stagger_free ? 0ull : static_cast<unsigned long long>(slot - p.stagger_free + 1) * p.stagger_ns;
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < wait_ns) __nanosleep(100);
+  }
   const float rcp6 = rcp_approx_ftz(6.0f);
   const uint8_t* xrow = p.x + static_cast<int64_t>(row) * p.H * 2;
   uint32_t c[VBMAX][V * 4];  // block b of this thread: chunks V*q + i + b*TPR, i < V
@@ -406,6 +433,7 @@ __global__ void __launch_bounds__(128) rmsnorm_fp4quant_block_kernel(const __gri
       p.pow2 ? __fmaf_rn(sum, p.inv_h, p.eps) : add_f32(__fdiv_rn(sum, static_cast<float>(p.H)), p.eps);
   const float rstd = rsqrt_approx_ftz(shifted);
   const float gs = p.use_e4m3 ? *p.gs : 0.0f;
+  if (p.timeline && tid == 0) p.timeline[blockIdx.x * 4 + 1] = global_timer_ns();
   if (!row_valid) return;
 
   const uint8_t* wbase = p.w;
@@ -453,6 +481,7 @@ __global__ void __launch_bounds__(128) rmsnorm_fp4quant_block_kernel(const __gri
     }
   }
   if (p.enable_pdl) pdl_launch_dependents();
+  if (p.timeline && tid == 0) p.timeline[blockIdx.x * 4 + 2] = global_timer_ns();
 }
 
 // ---- rows spread over a thread-block cluster (rmsnorm_fp4quant.py kernel_body :857-891) ----------
@@ -618,10 +647,32 @@ int g_block_owner = [] {
 
 // Tuning knob: B2_RMSNORM_PREFETCH = 0 switches the block-owner kernel's look-ahead prefetch off, N > 0
 // sets its distance to N CTAs; default: half the CTAs resident on the device at once (measured at
-// 8192 x 7168 with cold inputs: off 35.2 us, a quarter or half a generation 33.4-33.8 us, a whole one 36.0 us).
+// 8192 x 7168 with cold inputs: off 35.2 us, a quarter or half a generation 33.4-33.8 us, a whole one 36.0 us),
+// a third for the rows that also get the start offset below (29.6 against 29.7 us, 34.8 against 35.2 at 8192 x 8192).
 int g_prefetch = [] {
   const char* v = getenv("B2_RMSNORM_PREFETCH");
   return v ? atoi(v) : -1;
+}();
+
+// Tuning knob: B2_RMSNORM_STAGGER_NS = start offset, in nanoseconds, between the CTAs that share an SM at
+// launch (block-owner kernel; 0 = all start together; default: 1500 for rows of 7 or 8 scale blocks per
+// thread, none otherwise).  Measured at 8192 x 7168 with cold inputs: the CTAs resident at launch all wait
+// ~6 us for their rows (888 CTAs ask for 25 MB at once), then all quantize for ~4 us with HBM idle; with the
+// k-th CTA of every SM starting 1.5 k us late the steady mix of loading and quantizing CTAs is reached 2 us
+// earlier: 31.5 -> 29.6 us (800 ns: 31.4, 1200: 30.4, 2000: 30.8; letting two or three CTAs per SM start at
+// once: no gain at any offset).  Rows of 4096 values lose 3 % with it.
+int g_stagger_ns = [] {
+  const char* v = getenv("B2_RMSNORM_STAGGER_NS");
+  return v ? atoi(v) : -1;
+}();
+
+// Device buffer of the per-CTA timeline (b2_rmsnorm_fp4quant_timeline); null = not recording.
+std::atomic<unsigned long long*> g_timeline{nullptr};
+
+// B2_RMSNORM_STAGGER_FREE = CTAs per SM that start without an offset (default 1).
+int g_stagger_free = [] {
+  const char* v = getenv("B2_RMSNORM_STAGGER_FREE");
+  return v ? atoi(v) : 1;
 }();
 
 template <typename Kernel>
@@ -643,7 +694,7 @@ int launch_config(Kernel kernel, const RmsParams& p, int rows_per_cta, int threa
 }
 
 template <typename Kernel>
-int launch_block_owner(Kernel kernel, RmsParams p, int rows_per_cta, cudaStream_t stream) {
+int launch_block_owner(Kernel kernel, RmsParams p, int rows_per_cta, cudaStream_t stream, bool long_rows = false) {
   static int resident = 0;  // per instantiation
   if (resident == 0) {
     int per_sm = 0;
@@ -651,7 +702,15 @@ int launch_block_owner(Kernel kernel, RmsParams p, int rows_per_cta, cudaStream_
     const int sms = device_sm_count();
     resident = std::max(2, per_sm * std::max(sms, 1));
   }
-  p.prefetch_ctas = g_prefetch < 0 ? resident / 2 : g_prefetch;
+  p.prefetch_ctas = g_prefetch < 0 ? (long_rows ? resident / 3 : resident / 2) : g_prefetch;
+  // (only where at least two generations of CTAs follow one another: a launch that fits the GPU at once
+  // would merely start late)
+  const int grid = (p.M + rows_per_cta - 1) / rows_per_cta;
+  p.stagger_ns = g_stagger_ns < 0 ? (long_rows && grid >= 2 * resident ? 1500 : 0) : g_stagger_ns;
+  p.first_ctas = resident;
+  p.stagger_free = g_stagger_free;
+  p.timeline = g_timeline.load(std::memory_order_relaxed);
+  p.sm_count = std::max(device_sm_count(), 1);
   return launch_config(kernel, p, rows_per_cta, 128, 0, stream);
 }
 
@@ -671,11 +730,12 @@ int launch(const RmsParams& p, cudaStream_t stream) {
       if constexpr (kV == 2) {
         if (p.vb <= 4) return launch_block_owner(rmsnorm_fp4quant_block_kernel<Tag, TPR, BLOCK, 4>, p, 128 / kP, stream);
         if (p.vb <= 6) return launch_block_owner(rmsnorm_fp4quant_block_kernel<Tag, TPR, BLOCK, 6>, p, 128 / kP, stream);
-        if (p.vb == 7) return launch_block_owner(rmsnorm_fp4quant_block_kernel<Tag, TPR, BLOCK, 7>, p, 128 / kP, stream);
+        if (p.vb == 7) return launch_block_owner(rmsnorm_fp4quant_block_kernel<Tag, TPR, BLOCK, 7>, p, 128 / kP, stream, TPR >= 128);
       } else {
         if (p.vb <= 2) return launch_block_owner(rmsnorm_fp4quant_block_kernel<Tag, TPR, BLOCK, 2>, p, 128 / kP, stream);
       }
-      return launch_block_owner(rmsnorm_fp4quant_block_kernel<Tag, TPR, BLOCK, kBlockVb>, p, 128 / kP, stream);
+      return launch_block_owner(rmsnorm_fp4quant_block_kernel<Tag, TPR, BLOCK, kBlockVb>, p, 128 / kP, stream,
+                                kV == 2 && TPR >= 128 && p.vb == 8);
     }
     if ((p.H >> 3) == p.vb * TPR && p.vb <= 16) {
       if (p.vb <= 8) return launch_config(rmsnorm_fp4quant_reg_kernel<Tag, TPR, BLOCK, 8>, p, kRows, kThreads, 0, stream);
@@ -779,6 +839,11 @@ extern "C" int b2_rmsnorm_fp4quant(const void* x, const void* w, void* y, void* 
   p.inv_h = 1.0f / static_cast<float>(H);
   p.enable_pdl = enable_pdl ? 1 : 0;
   p.prefetch_ctas = 0;
+  p.stagger_ns = 0;
+  p.first_ctas = 0;
+  p.sm_count = 1;
+  p.stagger_free = 1;
+  p.timeline = nullptr;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int cluster_n = source_cluster_n(H);
   if (cluster_n > 1) {
@@ -799,4 +864,13 @@ extern "C" int b2_rmsnorm_fp4quant(const void* x, const void* w, void* y, void* 
   }
   if (in_dtype == B2_DTYPE_F16) return dispatch_block<F16Tag>(p, tpr, s);
   return dispatch_block<BF16Tag>(p, tpr, s);
+}
+
+// Observability: while `device_buf` is non-null, launches of the register-resident (block-owner) kernel
+// record, per CTA, four 64-bit words at device_buf[4 * cta]: start, row sums reduced, end (nanoseconds of
+// the GPU's global timer) and the SM the CTA ran on.  The buffer must hold 4 * ceil(M / rows per CTA)
+// words (4 * M is always enough); pass null to stop recording.
+extern "C" int b2_rmsnorm_fp4quant_timeline(unsigned long long* device_buf) {
+  b2::g_timeline.store(device_buf, std::memory_order_relaxed);
+  return B2_OK;
 }

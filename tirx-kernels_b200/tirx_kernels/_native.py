@@ -35,6 +35,7 @@ MAIN_SIGNATURES = {
     "b2_rmsnorm_fp4quant": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _vp]),
     "b2_add_rmsnorm_fp4quant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "b2_nvfp4_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "b2_rmsnorm_fp4quant_timeline": (_i, [_vp]),
     "b2_nvfp4_gemm_small_m_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "b2_nvfp4_gemm_status": (_i, [_vp]),
     "b2_nvfp4_gemm_small_m_noalloc_status": (_i, [_vp]),
