@@ -35,6 +35,7 @@ sys.path[:0] = [str(REPO / "tirx-kernels_b200"), str(REPO)]
 
 HEADLINE = {"dtype": "bfloat16", "m": 16384, "k": 7168, "sf_layout": "128x4"}
 METRIC = "nvfp4_quantize HBM throughput (16384x7168 bf16, 128x4 SF, 0.1% outliers); nvfp4_gemm TFLOPS under extra"
+WORKLOAD = "nvfp4_quantize bf16_128x4_m16384_k7168 (0.1% outliers x50), one batch per GPU"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel (mean of the two
 # launches of the ncu summary kept under profiles/ for this kernel and shape: 234.95 MB read + ~13.3 MB written
 # inside the kernel window; the rest of the 66 MB of output is still dirty in L2 when it ends).
@@ -196,6 +197,7 @@ def run_ours(args) -> dict:
         sf_pin.copy_(sf, non_blocking=True)
 
     e2e_steps = max(3, min(args.steps, 10))
+    copy_rates = host_copy_rates(x, x_pin, out, out_pin, sf, sf_pin, distributed)
     serial_ms = timed_region(e2e_step, e2e_steps, 2, distributed) / e2e_steps
     # the same through the host-buffer pipeline of the package: row chunks on three streams, upload, kernel
     # and download overlapped (every byte still crosses PCIe inside the timed region)
@@ -209,13 +211,14 @@ def run_ours(args) -> dict:
            "h2d_bytes_per_step": x_pin.numel() * 2, "d2h_bytes_per_step": out_pin.numel() + sf_pin.numel(),
            "path": "HostQuantizePipeline: 8 row chunks, upload / kernel / download on three streams",
            "launches_per_step": pipeline.launches_per_call, "matches_device_path": pipelined_ok,
+           "host_copy_gbs_per_rank": copy_rates,
            "serial_copy_launch_copy": {"value": world * step_bytes / (serial_ms * 1e-3) / 1e9, "ms_per_step": serial_ms}}
 
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32 scale math on bf16 input, e2m1/e4m3 output", "data": "synthetic",
-        "config": {"workload": "nvfp4_quantize bf16_128x4_m16384_k7168 (0.1% outliers x50), one batch per GPU",
+        "config": {"workload": WORKLOAD,
                    "l2": "inputs larger than L2: 301 MB touched per step, no flush needed",
                    "algorithmic_bytes_per_step": step_bytes},
         "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
@@ -224,10 +227,45 @@ def run_ours(args) -> dict:
         line["cpu_baseline"] = cpu_baseline(x_host, float(gs_host.item()), layout, budget_s=8.0)
     if not args.no_extra:
         line["extra"] = extras(args, rank, world, distributed)
+        summary = line["extra"].get("ffn_gate_up_tp", {}).get("scaling_summary")
+        if summary:  # last key of the line: the sharded projection against one GPU of the same box
+            line["ffn_gate_up_tp"] = summary
     if distributed:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
     return line if rank == 0 else {}
+
+
+def host_copy_rates(x, x_pin, out, out_pin, sf, sf_pin, distributed: bool) -> dict:
+    """Pinned-memory copy rates of every rank, all ranks copying at the same time (GB/s): what the end-to-end
+    leg can reach when N ranks share the host's PCIe and memory fabric."""
+    import torch
+
+    def one_way(fn, nbytes):
+        if distributed:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(3):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return 3 * nbytes / (start.elapsed_time(end) * 1e-3) / 1e9
+
+    def download():
+        out_pin.copy_(out, non_blocking=True)
+        sf_pin.copy_(sf, non_blocking=True)
+
+    h2d = one_way(lambda: x.copy_(x_pin, non_blocking=True), x_pin.numel() * 2)
+    d2h = one_way(download, out_pin.numel() + sf_pin.numel())
+    rates = torch.tensor([h2d, d2h], dtype=torch.float64, device="cuda")
+    if distributed:
+        gathered = [torch.zeros_like(rates) for _ in range(torch.distributed.get_world_size())]
+        torch.distributed.all_gather(gathered, rates)
+    else:
+        gathered = [rates]
+    return {"h2d": [round(float(g[0]), 1) for g in gathered], "d2h": [round(float(g[1]), 1) for g in gathered]}
 
 
 def cpu_baseline(x_host, gs: float, layout: str, budget_s: float, steps: int | None = None) -> dict:
@@ -387,6 +425,7 @@ def extras(args, rank: int, world: int, distributed: bool) -> dict:
             if M > 16:
                 us = _bench_us(lambda: exg(A_fp4, B_fp4, A_sf, B_sf, alpha_t, D), reps=20)
                 entry = {"us": us, "tflops": gemm.flops(M, N, K) / us / 1e6}
+                entry.update(gemm_role_timers(lambda: exg(A_fp4, B_fp4, A_sf, B_sf, alpha_t, D), K, us))
             else:
                 # decode: weights (36 MB) fit in L2, so rotate over sixteen copies (570 MB) inside a CUDA graph
                 copies = [(B_fp4.clone(), B_sf.clone()) for _ in range(16)]
@@ -413,6 +452,35 @@ def extras(args, rank: int, world: int, distributed: bool) -> dict:
             del A_fp4, B_fp4, A_sf, B_sf, D
     out["ffn_gate_up_tp"] = ffn_sharded(rank, world, distributed)
     return out
+
+
+def gemm_role_timers(launch, K: int, us: float) -> dict:
+    """In-kernel role timers of one more launch (CTA 0): where the MMA role's time goes per 256-wide K slab
+    and per tile, the SM clock the kernel saw, and the launch time normalised by that clock (the GEMM runs
+    under the power cap: a slower clock and a slower kernel are told apart by `us_x_sm_ghz`)."""
+    import ctypes
+
+    import torch
+
+    from tirx_kernels import _native
+
+    lib = _native.lib()
+    _native.check(lib.b2_nvfp4_gemm_role_timers(1, None, None), "b2_nvfp4_gemm_role_timers")
+    launch()
+    torch.cuda.synchronize()
+    out = (ctypes.c_ulonglong * 12)()
+    _native.check(lib.b2_nvfp4_gemm_role_timers(0, out, None), "b2_nvfp4_gemm_role_timers")
+    t = [int(v) for v in out]
+    tiles, slabs = max(t[8], 1), max(t[8], 1) * (K // 256)
+    ghz = t[4] / max(t[11], 1)
+    return {"role_timers_cta0": {
+        "tiles": t[8], "cycles_per_k_slab": round(t[4] / slabs, 1),
+        "mma_issue_cycles_per_k_slab": round(t[5] / slabs, 1),
+        "mma_wait_for_operands_and_scales_per_k_slab": round(t[2] / slabs, 1),
+        "mma_wait_for_drained_accumulator_per_tile": round(t[3] / tiles, 1),
+        "epilogue_body_cycles_per_tile": round(t[7] / tiles, 1),
+        "tensor_cycles_needed_per_k_slab": 512, "sm_ghz_in_kernel": round(ghz, 3)},
+        "us_x_sm_ghz": round(us * ghz, 1)}
 
 
 def ffn_sharded(rank: int, world: int, distributed: bool, M: int = 8192, N: int = 28672, K: int = 8192) -> dict:
@@ -521,6 +589,43 @@ def ffn_sharded(rank: int, world: int, distributed: bool, M: int = 8192, N: int 
         received = (world - 1) * M * shard * 2
         result["allgather_recv_gbs"] = received / t_ag / 1e3
         result["allgather_frac_of_770gbs_peer_copy"] = result["allgather_recv_gbs"] / 770.0
+        # the unsharded projection on one GPU of this very box (rank 0; the others wait): the denominator
+        # of every strong-scaling figure below
+        single = torch.zeros(3, dtype=torch.float64, device="cuda")
+        if rank == 0:
+            gw = torch.Generator(device="cuda").manual_seed(1000)
+            w_full = (0.02 * torch.randn(N, K, device="cuda", dtype=torch.float32, generator=gw)).to(torch.bfloat16)
+            Bf, Bs = gemm.quantize_operand(w_full, 2688.0 / w_full.float().abs().max().reshape(1))
+            del w_full
+            Df = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+            exf = gemm._compile_executable(M, N, K)
+
+            def full_step():
+                quantize()
+                exf(A_fp4, Bf, A_sf, Bs, alpha_t, Df)
+
+            single[0] = timed_region(lambda: exf(A_fp4, Bf, A_sf, Bs, alpha_t, Df), 10, 3, False) / 10 * 1e3
+            single[1] = timed_region(full_step, 10, 3, False) / 10 * 1e3
+            single[2] = timed_region(quantize, 10, 3, False) / 10 * 1e3
+            _native.nvfp4_gemm_status()
+            del Bf, Bs, Df
+        torch.distributed.barrier()
+        torch.distributed.broadcast(single, src=0)
+        g1, s1, q1 = (float(v) for v in single)
+        # what the exchange allows: every GPU must receive (world-1)/world of the bf16 output over NVLink, at
+        # best at the peer-copy rate measured on this pool (770 GB/s per direction), hidden behind the GEMM
+        exchange_us = received / 770.0 / 1e3
+        bound_step = q1 + max(g1 / world, exchange_us)
+        result["single_gpu"] = {"gemm_us": g1, "step_us": s1, "quantize_us": q1}
+        result["scaling_summary"] = {
+            "gpus": world,
+            "nccl_path": {"step_us": t_all, "speedup_vs_1gpu": s1 / t_all, "of_linear": s1 / t_all / world},
+            "fused_path": {"step_us": t_fall, "speedup_vs_1gpu": s1 / t_fall, "of_linear": s1 / t_fall / world},
+            "gemm_phase_of_linear": g1 / t_g / world,
+            "bound_at_measured_peer_copy": {"exchange_us": exchange_us, "step_us": bound_step,
+                                            "speedup_vs_1gpu": s1 / bound_step},
+            "fused_step_over_bound": t_fall / bound_step,
+        }
     return result
 
 
@@ -538,9 +643,9 @@ def run_reference(args) -> dict:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32 scale math on bf16 input, e2m1/e4m3 output",
         "data": "synthetic",
-        "config": {"workload": "nvfp4_quantize bf16_128x4_m16384_k7168 (0.1% outliers x50) on the host cores",
+        "config": {"workload": WORKLOAD,
                    "note": "the reference's GPU kernels need the TIRx compiler (tvm.tirx), absent here; this is "
-                           "the CPU restatement of its arithmetic, rank 0 only"},
+                           "the CPU restatement of its arithmetic on the host cores, rank 0 only"},
         "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,

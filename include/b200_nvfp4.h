@@ -167,7 +167,8 @@ int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, const void* SFB
 /* Selects the kernel variant used by the following b2_nvfp4_gemm calls of this process
  * (-1 restores automatic selection): 0 single CTA / N tile 128, 1 single CTA / N tile 256,
  * 2 CTA pair / N tile 256, 3 CTA pair / N tile 128, 4 and 5 = 0 and 1 for M <= 32 (32 rows of A
- * per stage, deeper ring).  The reference fixes its tiling per
+ * per stage, deeper ring), 6 = M <= 32 with N tile 64 and all of K per CTA, 7 = 6 with two MMA-issuing
+ * warps (two accumulators, added in the epilogue).  The reference fixes its tiling per
  * shape in TIRX_CONFIGS, tirx_kernels/basic/nvfp4_gemm.py:860-903; this is the matching knob. */
 int b2_nvfp4_gemm_set_variant(int variant);
 

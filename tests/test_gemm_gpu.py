@@ -25,14 +25,14 @@ SMALL_SHAPES = [(128, 128, 256), (256, 256, 256), (384, 640, 768), (1024, 1024, 
                 (200, 384, 512), (1, 256, 4096), (32, 1024, 8192), (7, 768, 2304)]
 
 
-@pytest.mark.parametrize("which", [0, 1, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("which", [0, 1, 2, 3, 4, 5, 6, 7])
 @pytest.mark.parametrize("M,N,K", SMALL_SHAPES)
 def test_every_variant_matches_the_oracle(which, M, N, K, variant, native):
     import oracle_provider
 
     if which in (1, 2, 5) and N % 256:
         pytest.skip("variant needs N % 256 == 0")
-    if which in (4, 5, 6) and M > 32:
+    if which in (4, 5, 6, 7) and M > 32:
         pytest.skip("variant needs M <= 32")
     mod = _module()
     A_fp4, B_fp4, A_sf, B_sf, alpha, _ = mod.prepare_data(M, N, K)
@@ -171,3 +171,30 @@ def test_invalid_shapes_are_rejected_before_launch(native):
     with pytest.raises(ValueError, match="K % 256"):
         native.nvfp4_gemm(z, z, z, z, torch.ones(1, device="cuda"), torch.empty(16, dtype=torch.bfloat16, device="cuda"),
                           4, 128, 200)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_process_drives_two_devices(native):
+    """The kernels' shared-memory attribute, the status words and the split-K scratch are kept per device:
+    the same process launches every kind of variant on a second GPU and gets the same bits."""
+    mod = _module()
+    for M, N, K in ((512, 512, 1024), (16, 1024, 4096), (100, 384, 512)):
+        A_fp4, B_fp4, A_sf, B_sf, alpha, _ = mod.prepare_data(M, N, K)
+        alpha_t = torch.tensor([float(alpha)], device="cuda:0")
+        first = torch.empty(M, N, dtype=torch.bfloat16, device="cuda:0")
+        native.nvfp4_gemm(A_fp4, B_fp4, A_sf, B_sf, alpha_t, first, M, N, K)
+        torch.cuda.synchronize(0)
+        native.nvfp4_gemm_status()
+        with torch.cuda.device(1):
+            moved = [t.to("cuda:1") for t in (A_fp4, B_fp4, A_sf, B_sf, alpha_t)]
+            second = torch.empty(M, N, dtype=torch.bfloat16, device="cuda:1")
+            native.nvfp4_gemm(*moved, second, M, N, K)
+            torch.cuda.synchronize(1)
+            native.nvfp4_gemm_status()
+            small = torch.empty(M, N, dtype=torch.bfloat16, device="cuda:1")
+            if M <= 128:
+                native.nvfp4_gemm_small_m_noalloc(*moved, small, M, N, K)
+                torch.cuda.synchronize(1)
+                native.nvfp4_gemm_small_m_noalloc_status()
+                assert torch.equal(small, second)
+        assert torch.equal(first.cpu(), second.cpu())

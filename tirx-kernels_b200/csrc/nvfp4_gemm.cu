@@ -380,12 +380,21 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-template <int CG, int BN, int STAGES, int TMA_OUT, int AM>
-__global__ void __launch_bounds__(kThreads, 1)
+// MMAS: MMA-issuing warps.  Issuing one tcgen05.mma costs its thread about 75 cycles whatever the tile
+// width, so a decode-sized problem that gives every CTA a narrow tile and all of K (no K ranges, no second
+// kernel) is bound by that one thread: 128 MMAs of N = 64 take it longer than HBM takes to deliver the
+// weights.  With MMAS == 2 a second warp issues the odd K slabs into a second accumulator (columns
+// [BN, 2 BN) of tensor memory) and the epilogue adds the two.
+template <int CG, int BN, int STAGES, int TMA_OUT, int AM, int MMAS>
+__global__ void __launch_bounds__(kThreads + 32 * (MMAS - 1), 1)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                       const __grid_constant__ GemmParams p, const __grid_constant__ OutMaps<(TMA_OUT > 0)> out_maps) {
   using L = SmemLayout<CG, BN, STAGES, TMA_OUT, AM>;
+  static_assert(MMAS == 1 || (MMAS == 2 && CG == 1 && TMA_OUT == 0), "the second MMA warp exists for single-CTA tiles");
+  static_assert(BN * MMAS + STAGES * L::kSfCols <= 512, "tensor memory budget");
+  constexpr int kAccCols = BN * MMAS;  // accumulator columns in front of the stages' scale areas
+  constexpr int kWarpMma2 = 19;
   constexpr int kTmemCols = 512;
   constexpr uint32_t kIdesc = instr_desc(kBlockM * CG, BN);
   constexpr uint32_t kOperandTx = static_cast<uint32_t>(L::kABytes + L::kBBytes) * CG;
@@ -425,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(sfload_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(tmem_full_bar, 1);
+    mbar_init(tmem_full_bar, MMAS);
     mbar_init(tmem_empty_bar, 8 * CG);  // one arrive per epilogue warp of every CTA in the group
     *abort_flag = 0u;
     fence_barrier_init();
@@ -480,18 +489,23 @@ __global__ void __launch_bounds__(kThreads, 1)
         counters[1] = clock64() - t_begin;
       }
     }
-  } else if (warp == kWarpMma) {
-    // ================= MMA issuer (leader CTA only) =================
+  } else if (warp == kWarpMma || (MMAS == 2 && warp == kWarpMma2)) {
+    // ================= MMA issuer(s) (leader CTA only) =================
+    // Issuer `me` of MMAS takes the K slabs with (slab index in the tile) % MMAS == me and accumulates them
+    // in its own tensor-memory columns.
+    const int me = warp == kWarpMma ? 0 : 1;
     if (leader && lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0, acc_phase = 0;
+      uint32_t acc_phase = 0;
       bool alive = true;
-      long long t_full = 0, t_acc = 0, t_issue = 0, t_begin = prof ? clock64() : 0;
-      const uint64_t ns_begin = prof ? globaltimer_ns() : 0;
-      for (int t = unit; t < num_tiles && alive; t += num_units) {
-        const long long a0 = prof ? clock64() : 0;
+      int slab0 = 0;  // slabs of the tiles this CTA has finished: the ring position of the tile's first slab
+      const bool mprof = prof && me == 0;
+      long long t_full = 0, t_acc = 0, t_issue = 0, t_begin = mprof ? clock64() : 0;
+      const uint64_t ns_begin = mprof ? globaltimer_ns() : 0;
+      const uint32_t acc_tmem = tmem_base + static_cast<uint32_t>(me * BN);
+      for (int t = unit; t < num_tiles && alive; t += num_units, slab0 += k_slabs) {
+        const long long a0 = mprof ? clock64() : 0;
         if (!wait_or_abort<kClusterAcquireWaits && CG == 2>(tmem_empty_bar, acc_phase ^ 1u, ctx, 2u)) break;
-        if (prof) t_acc += clock64() - a0;
+        if (mprof) t_acc += clock64() - a0;
         tc_fence_after();
         // A 64-wide tile uses half of a 128-row scale chunk of B: the MMA reads N / 32 scale columns from
         // the address it is given, so the upper half starts two columns in.
@@ -501,33 +515,35 @@ __global__ void __launch_bounds__(kThreads, 1)
           tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
           sfb_half = static_cast<uint32_t>(tn & 1) * 2u;
         }
-        for (int ks = 0; ks < k_slabs; ++ks) {
-          const long long w0 = prof ? clock64() : 0;
+        for (int ks = me; ks < k_slabs; ks += MMAS) {
+          const int n = slab0 + ks;
+          const int stage = n % STAGES;
+          const uint32_t phase = static_cast<uint32_t>(n / STAGES) & 1u;
+          const long long w0 = mprof ? clock64() : 0;
           if (!wait_or_abort<kClusterAcquireWaits && CG == 2>(full_bar(stage), phase, ctx, 3u)) { alive = false; break; }
-          const long long w1 = prof ? clock64() : 0;
+          const long long w1 = mprof ? clock64() : 0;
           t_full += w1 - w0;
           tc_fence_after();
           const uint32_t sbase = smem_base + stage * L::kStageBytes;
-          const uint32_t sf_tmem = tmem_base + BN + stage * L::kSfCols;
+          const uint32_t sf_tmem = tmem_base + kAccCols + stage * L::kSfCols;
           const uint64_t a_desc = operand_desc(sbase);
           const uint64_t b_desc = operand_desc(sbase + L::kABytes);
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) {
             // 64 fp4 values = 32 bytes = 2 descriptor address units inside the swizzled row
-            tc_mma<CG>(tmem_base, a_desc + 2 * kb, b_desc + 2 * kb, kIdesc, sf_tmem + kb * 4,
-                       sf_tmem + 16 + kb * 4 * L::kChunks + sfb_half, (ks | kb) ? 1u : 0u);
+            tc_mma<CG>(acc_tmem, a_desc + 2 * kb, b_desc + 2 * kb, kIdesc, sf_tmem + kb * 4,
+                       sf_tmem + 16 + kb * 4 * L::kChunks + sfb_half, (ks >= MMAS || kb) ? 1u : 0u);
           }
           if constexpr (CG == 2) tc_commit_pair(empty_bar(stage));
           else tc_commit<CG>(empty_bar(stage));
-          if (prof) t_issue += clock64() - w1;
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (mprof) t_issue += clock64() - w1;
         }
         if (!alive) break;
         if constexpr (CG == 2) tc_commit_pair(tmem_full_bar);
         else tc_commit<CG>(tmem_full_bar);
         acc_phase ^= 1u;
       }
-      if (prof) {
+      if (mprof) {
         counters[2] = t_full;
         counters[3] = t_acc;
         counters[4] = clock64() - t_begin;
@@ -567,7 +583,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int kb = 0; kb < 4; ++kb)
 #pragma unroll
         for (int c = 0; c < L::kChunks; ++c) lds128(sfb_smem + (c * 4 + kb) * 512, b + 4 * (kb * L::kChunks + c));
-      const uint32_t dst = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + BN + stage * L::kSfCols;
+      const uint32_t dst = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kAccCols + stage * L::kSfCols;
       tmem_st_32x32_x16(dst, a);
 #pragma unroll
       for (int c = 0; c < L::kChunks; ++c) tmem_st_32x32_x16(dst + 16 + 16 * c, b + 16 * c);
@@ -618,6 +634,21 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t empty_target = CG == 2 ? mapa_shared(tmem_empty_bar, 0) : tmem_empty_bar;
     const bool eprof = prof && warp == kWarpEpi0;
     long long t_wait = 0, t_body = 0, n_tiles = 0;
+    // 32 accumulator columns of this warp's lane quarter, starting at tile column `col` (with two MMA
+    // warps: the sum of their two accumulators)
+    auto drain32 = [&](int col, uint32_t (&v)[32]) {
+      const uint32_t addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + col;
+      tmem_ld_32x32(addr, v);
+      if constexpr (MMAS == 2) {
+        uint32_t v2[32];
+        tmem_ld_32x32(addr + BN, v2);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(v2[i]));
+      } else {
+        tmem_ld_wait();
+      }
+    };
     for (int t = unit; t < num_tiles; t += num_units) {
       int tm, tn;
       tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
@@ -641,8 +672,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll 1
           for (int c0 = 0; c0 < kHalf; c0 += 32) {
             uint32_t v[32];
-            tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * kHalf + c0, v);
-            tmem_ld_wait();
+            drain32(half * kHalf + c0, v);
             if (row < p.M) {
               uint4* dst = reinterpret_cast<uint4*>(prow + c0);
 #pragma unroll
@@ -673,8 +703,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int c0 = 0; c0 < kHalf; c0 += 32) {
           uint32_t v[32];
-          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * kHalf + c0, v);
-          tmem_ld_wait();
+          drain32(half * kHalf + c0, v);
 #pragma unroll
           for (int i = 0; i < 16; ++i)
             packed[c0 / 2 + i] = pack_from_f32<BF16Tag>(__uint_as_float(v[2 * i]) * alpha,
@@ -714,8 +743,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
       for (int c0 = 0; c0 < kHalf; c0 += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * kHalf + c0, v);
-        tmem_ld_wait();
+        drain32(half * kHalf + c0, v);
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           packed[c0 / 2 + i] = pack_from_f32<BF16Tag>(__uint_as_float(v[2 * i]) * alpha,
@@ -926,12 +954,12 @@ int encode_output_map(CUtensorMap* map, void* base, int M, int ldd) {
   return B2_OK;
 }
 
-template <int CG, int BN, int STAGES, int TMA_OUT = 0, int AM = kBlockM>
+template <int CG, int BN, int STAGES, int TMA_OUT = 0, int AM = kBlockM, int MMAS = 1>
 int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N, int K, int splits,
                    uint32_t* status, float* partial, cudaStream_t stream, const GatherTarget& gather = GatherTarget(),
                    const OutMaps<(TMA_OUT > 0)>& out_maps = OutMaps<(TMA_OUT > 0)>()) {
   using L = SmemLayout<CG, BN, STAGES, TMA_OUT, AM>;
-  auto kernel = nvfp4_gemm_kernel<CG, BN, STAGES, TMA_OUT, AM>;
+  auto kernel = nvfp4_gemm_kernel<CG, BN, STAGES, TMA_OUT, AM, MMAS>;
   GemmParams p;
   p.alpha = alpha;
   p.D = static_cast<uint16_t*>(D);
@@ -973,7 +1001,7 @@ int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(units * CG);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(kThreads + 32 * (MMAS - 1));
   cfg.dynamicSmemBytes = L::kTotal;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -1057,7 +1085,7 @@ struct FixedWorkspace {
   const char* who;
 };
 
-template <int CG, int BN, int STAGES, int TMA_OUT = 0, int AM = kBlockM>
+template <int CG, int BN, int STAGES, int TMA_OUT = 0, int AM = kBlockM, int MMAS = 1>
 int launch_variant(const void* A, const void* B, const void* SFA, const void* SFB, const float* alpha,
                    void* D, int M, int N, int K, int variant, cudaStream_t stream,
                    const FixedWorkspace* fixed = nullptr) {
@@ -1114,7 +1142,7 @@ int launch_variant(const void* A, const void* B, const void* SFA, const void* SF
     return launch_kernels<CG, BN, STAGES, TMA_OUT>(maps, alpha, D, M, N, K, splits, status, partial, stream, target,
                                                 out_maps);
   } else {
-    return launch_kernels<CG, BN, STAGES, 0, AM>(maps, alpha, D, M, N, K, splits, status, partial, stream);
+    return launch_kernels<CG, BN, STAGES, 0, AM, MMAS>(maps, alpha, D, M, N, K, splits, status, partial, stream);
   }
 }
 
@@ -1127,6 +1155,9 @@ int choose_variant(int M, int N, int K) {
     // Decode-sized M: single-CTA tiles and K ranges to fill the GPU.  The time goes with the slabs
     // one CTA runs in series (waves x slabs per work item); a 256-wide slab costs about 1.8 of a
     // 128-wide one, and its four-fold partial sums only pay off while M is small.
+    // M <= 32 and no more 64-wide tiles than SMs: every CTA takes one tile and all of K, two warps issue
+    // its MMAs; no K ranges, no second kernel (16 x 8192 x 8192: 11.8 us against 13.1 with K ranges).
+    if (sms > 0 && M <= 32 && N / 64 <= sms && K >= 512) return 7;
     int variant = 0;
     if (sms > 0 && M <= 32 && N % 256 == 0) {
       const int k_slabs = K / kBlockK;
@@ -1155,9 +1186,10 @@ int choose_variant(int M, int N, int K) {
 // Selects a kernel variant for the following calls of this process (-1 restores automatic
 // selection).  0: single CTA, N tile 128; 1: single CTA, N tile 256; 2: CTA pair, N tile 256;
 // 3: CTA pair, N tile 128; 4 and 5: 0 and 1 for M <= 32, loading 32 rows of A per stage into a deeper
-// ring.  Used by the tests to exercise every variant on small shapes.
+// ring; 6: M <= 32, N tile 64; 7: 6 with two MMA-issuing warps.  Used by the tests to exercise every variant
+// on small shapes.
 extern "C" int b2_nvfp4_gemm_set_variant(int variant) {
-  if (variant < -1 || variant > 6) {
+  if (variant < -1 || variant > 7) {
     b2::set_error("b2_nvfp4_gemm_set_variant: unknown variant %d", variant);
     return B2_ERR_INVALID_ARGUMENT;
   }
@@ -1190,7 +1222,8 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int variant = g_forced_variant.load(std::memory_order_relaxed);
   if (variant < 0) variant = choose_variant(M, N, K);
-  if ((variant == 4 || variant == 5 || variant == 6) && M > 32) {
+  if (variant == 7 && K < 512) variant = 6;  // the second MMA warp needs a K slab of its own
+  if ((variant == 4 || variant == 5 || variant == 6 || variant == 7) && M > 32) {
     set_error("b2_nvfp4_gemm: variant %d needs M <= 32", variant);
     return B2_ERR_INVALID_ARGUMENT;
   }
@@ -1205,6 +1238,7 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
     case 4: return launch_variant<1, 128, 9, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 4, s);
     case 5: return launch_variant<1, 256, 5, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 5, s);
     case 6: return launch_variant<1, 64, 13, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 6, s);
+    case 7: return launch_variant<1, 64, 11, 0, 32, 2>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 7, s);
     default: return launch_variant<2, 128, 6, 1>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
   }
 }
@@ -1347,6 +1381,7 @@ extern "C" int b2_nvfp4_gemm_small_m_noalloc(const void* A, const void* B, const
     case 0: return launch_variant<1, 128, 6>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 0, s, &ws);
     case 1: return launch_variant<1, 256, 4>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 1, s, &ws);
     case 4: return launch_variant<1, 128, 9, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 4, s, &ws);
+    case 7: return launch_variant<1, 64, 11, 0, 32, 2>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 7, s, &ws);
     default: return launch_variant<1, 256, 5, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 5, s, &ws);
   }
 }

@@ -42,8 +42,9 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=None, help="Warm-up budget in ms")
     parser.add_argument("--repeat", type=int, default=None, help="Timed budget in ms")
     parser.add_argument("--timer", type=str, choices=TIMER_CHOICES, default=None,
-                        help="'event' (CUDA events, cold L2 per launch; default) or 'event_warm'; the "
-                             "remaining names belong to the reference's TVM timer and are rejected")
+                        help="'event' (CUDA events, cold L2 per launch; default), 'event_warm', 'proton' (kernel "
+                             "time from triton.profiler, cold L2) or 'cudagraph_proton' (the same over CUDA-graph "
+                             "replays); the remaining names belong to the reference's TVM timer and are rejected")
     parser.add_argument("--with-references", action="store_true",
                         help="Also time external library peers (cuBLASLt NVFP4)")
     parser.add_argument("--rounds", type=int, default=None, help="Independent timing rounds")

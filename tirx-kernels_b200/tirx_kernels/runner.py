@@ -12,7 +12,9 @@ Timing.  The reference delegates to ``tvm.tirx.bench.bench`` (Proton by default)
 buffer before it, so each launch starts with a cold, clean L2 - the conditions of the
 reference's protocol (25 ms warm-up, 100 ms repeat, 5 rounds, mean); launches of a few
 microseconds also carry the host's launch latency in this mode.  Timer ``event_warm`` times
-back-to-back launches between one pair of events.
+back-to-back launches between one pair of events.  Timers ``proton`` (cold L2, as ``event``) and
+``cudagraph_proton`` (launches replayed from a CUDA graph, warm L2) report pure kernel time from
+``triton.profiler``, the reference's default protocol.
 
 Late GPU assignment (``bind_cuda_assignment`` and friends, reference :347-449, :522-558)
 serves the bench suite's prepared-child protocol, see ``bench/_prepared_child.py``.
@@ -36,7 +38,7 @@ PREPARE_NUM_SMS_ENV = "TIRX_PREPARE_NUM_SMS"
 PREPARE_CUDA_ARCH_ENV = "TIRX_PREPARE_CUDA_ARCH"
 _EXTERNAL_REFERENCES_ENV = "TIRX_INTERNAL_BENCH_REFERENCES"
 L2_FLUSH_BYTES = 256 * 1024 * 1024
-SUPPORTED_TIMERS = ("event", "event_warm")
+SUPPORTED_TIMERS = ("event", "event_warm", "proton", "cudagraph_proton")
 
 
 # ---- external references (library peers timed beside our kernels) -------------------------
@@ -287,6 +289,68 @@ def _time_one(fn: Callable[[], Any], warmup_ms: float, repeat_ms: float, flush) 
     return _cold_ms(fn, min(n_repeat, 500), flush) * 1e3
 
 
+def _hatchet_kernel_ns(node, inside: bool, scope_name: str) -> float:
+    """Sum of the kernel times (ns) recorded below the scope `scope_name` in a Proton profile tree."""
+    frame = node.get("frame", {})
+    inside = inside or frame.get("name") == scope_name
+    total = 0.0
+    children = node.get("children", [])
+    if inside and not children:
+        total += float(node.get("metrics", {}).get("time (ns)", 0.0))
+    for child in children:
+        total += _hatchet_kernel_ns(child, inside, scope_name)
+    return total
+
+
+def _proton_us(fn: Callable[[], Any], n: int, flush, graph: bool) -> float:
+    """Mean kernel time of one launch of `fn` in microseconds as Proton (triton.profiler, CUPTI activity
+    records) sees it: pure device time of the kernels `fn` launches, no launch gaps and no host cost -
+    the protocol of the reference's `tvm.tirx.bench` (`proton`, and `cudagraph_proton`, which replays the
+    launches from a CUDA graph).  The L2 flush runs outside the profiled scope."""
+    import json
+    import tempfile
+
+    import torch
+
+    try:
+        import triton.profiler as proton
+    except Exception as error:
+        raise RuntimeError(f"timer 'proton' needs triton.profiler: {type(error).__name__}: {error}") from error
+    replay = None
+    if graph:
+        stream = torch.cuda.Stream()
+        cuda_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            fn()
+            stream.synchronize()
+            with torch.cuda.graph(cuda_graph, stream=stream):
+                fn()
+        replay = cuda_graph.replay
+    launch = replay or fn
+    with tempfile.TemporaryDirectory() as folder:
+        base = os.path.join(folder, "b2_proton")
+        session = proton.start(base, context="shadow", data="tree", backend="cupti")
+        try:
+            for _ in range(n):
+                if flush is not None:
+                    proton.deactivate(session)
+                    flush.sum()
+                    torch.cuda.synchronize()
+                    proton.activate(session)
+                with proton.scope("b2_timed"):
+                    launch()
+            torch.cuda.synchronize()
+        finally:
+            proton.finalize()
+        with open(base + ".hatchet") as handle:
+            tree = json.load(handle)
+    roots = tree if isinstance(tree, list) else [tree]
+    total_ns = sum(_hatchet_kernel_ns(root, False, "b2_timed") for root in roots)
+    if total_ns <= 0.0:
+        raise RuntimeError("Proton recorded no kernel time (CUPTI activity records unavailable on this machine?)")
+    return total_ns / n / 1e3
+
+
 def bench(funcs: Mapping[str, Callable[[], Any]], *, references: Mapping[str, Callable[[], Any]] | None = None,
           warmup: int | None = None, repeat: int | None = None, timer: str | None = None,
           rounds: int | None = None, cooldown_s: float | None = None, **_ignored: Any) -> dict[str, Any]:
@@ -299,9 +363,7 @@ def bench(funcs: Mapping[str, Callable[[], Any]], *, references: Mapping[str, Ca
 
     timer = timer or "event"
     if timer not in SUPPORTED_TIMERS:
-        raise ValueError(
-            f"timer {timer!r} needs the reference's tvm.tirx.bench; this build provides {SUPPORTED_TIMERS}"
-        )
+        raise ValueError(f"timer {timer!r} is not provided by this build; choose one of {SUPPORTED_TIMERS}")
     warmup_ms = DEFAULT_WARMUP_MS if warmup is None else warmup
     repeat_ms = DEFAULT_REPEAT_MS if repeat is None else repeat
     rounds = DEFAULT_BENCH_ROUNDS if rounds is None else rounds
@@ -316,14 +378,22 @@ def bench(funcs: Mapping[str, Callable[[], Any]], *, references: Mapping[str, Ca
             except Exception as error:  # a broken peer must not hide our own number
                 errors[name] = f"{type(error).__name__}: {error}"
     flush = None
-    if timer == "event":
+    if timer in ("event", "proton"):
         flush = torch.zeros(L2_FLUSH_BYTES // 8, dtype=torch.int64, device="cuda")
     samples: dict[str, list[float]] = {name: [] for name in launches}
     for _ in range(rounds):
         for name, fn in launches.items():
             if cooldown_s:
                 time.sleep(cooldown_s)
-            samples[name].append(_time_one(fn, warmup_ms, repeat_ms, flush))
+            if timer in ("proton", "cudagraph_proton"):
+                fn()
+                torch.cuda.synchronize()
+                estimate_ms = max(_chain_ms(fn, 5), 1e-3)
+                _chain_ms(fn, max(3, int(warmup_ms / estimate_ms)))
+                n_repeat = max(10, min(500, int(repeat_ms / estimate_ms)))
+                samples[name].append(_proton_us(fn, n_repeat, flush, graph=timer == "cudagraph_proton"))
+            else:
+                samples[name].append(_time_one(fn, warmup_ms, repeat_ms, flush))
     return {
         "impls": {name: statistics.fmean(values) for name, values in samples.items()},
         "round_samples": samples,
