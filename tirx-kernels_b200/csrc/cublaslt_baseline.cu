@@ -68,7 +68,9 @@ struct Plan {
 };
 
 std::mutex g_mu;
-std::map<std::tuple<int, int, int, int>, std::unique_ptr<Plan>> g_plans;
+// Plans live until the process exits and are deliberately never destroyed: a static destructor would call
+// into cuBLASLt and the CUDA runtime while those (and any attached profiler) are being torn down.
+auto& g_plans = *new std::map<std::tuple<int, int, int, int>, std::unique_ptr<Plan>>();
 
 }  // namespace
 

@@ -316,6 +316,7 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, con
     const uint64_t now = globaltimer_ns();
     if (started == 0) started = now;
     else if (now - started > budget) break;
+    if (i > (1u << 26)) break;  // backstop in polls, should the timer not advance (seconds at the shortest poll)
   }
   if (atomicCAS(ctx.status, 0u, code) == 0u) ctx.status[1] = blockIdx.x;
   *ctx.abort_flag = 1u;

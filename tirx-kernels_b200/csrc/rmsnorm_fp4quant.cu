@@ -343,8 +343,8 @@ __global__ void __launch_bounds__(128) rmsnorm_fp4quant_block_kernel(const __gri
   if (p.stagger_ns > 0 && static_cast<int>(blockIdx.x) < p.first_ctas) {
     const int slot = static_cast<int>(blockIdx.x) / p.sm_count;
     const unsigned long long wait_ns = slot < p.stagger_free ? 0ull : static_cast<unsigned long long>(slot - p.stagger_free + 1) * p.stagger_ns;
-    const unsigned long long t0 = global_timer_ns();
-    while (global_timer_ns() - t0 < wait_ns) __nanosleep(100);
+    // a fixed number of short sleeps: bounded whatever a timer does under a profiler
+    for (unsigned long long slept = 0; slept < wait_ns; slept += 128) __nanosleep(128);
   }
   const float rcp6 = rcp_approx_ftz(6.0f);
   const uint8_t* xrow = p.x + static_cast<int64_t>(row) * p.H * 2;
@@ -371,6 +371,16 @@ __global__ void __launch_bounds__(128) rmsnorm_fp4quant_block_kernel(const __gri
     } else {
 #pragma unroll
       for (int i = 0; i < V * 4; ++i) c[b][i] = 0u;
+    }
+  }
+  // The weights are needed only after the reduction; asking L2 for them now takes a cold miss off the
+  // critical path of a small launch (32 x 4096 with cold caches: 7.4 -> 5.3 us).  Only where all CTAs run at
+  // once: thousands of CTAs asking for the same 14 KB cost a large launch 25 %.
+  if (static_cast<int>(gridDim.x) <= p.first_ctas) {
+#pragma unroll
+    for (int b = 0; b < VBMAX; ++b) {
+      if (kExact || b < p.vb)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.w + static_cast<int64_t>(q + b * P) * V * 16));
     }
   }
   // Look-ahead: ask L2 for the rows of a CTA that starts about half a generation of resident CTAs
