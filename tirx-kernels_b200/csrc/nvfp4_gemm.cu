@@ -4,11 +4,14 @@
 // layout :47-66, :941-982; one E4M3 scale per 16 values along K, fp32 accumulation,
 // alpha then bf16 in the epilogue :795-800).  The kernel itself is written from scratch:
 //
-//   * persistent CTAs (or CTA pairs), one per SM, walking a grouped tile order;
-//   * warp 0: TMA producer  - A, B and both scale-factor blocks of a 256-wide K slab land in a
-//             ring of shared-memory stages, completion counted on mbarriers;
+//   * persistent CTAs (or CTA pairs), at most one per SM, walking a grouped tile order;
+//   * warp 0: TMA producer of A and B - the operands of a 256-wide K slab land in a ring of
+//             shared-memory stages, completion counted on mbarriers;
+//   * warp 18: TMA producer of the scale-factor blocks of the same slab (a thread of its own:
+//             issuing a TMA copy costs its thread on the order of a hundred cycles);
 //   * warp 1: MMA issuer    - four tcgen05.mma.kind::mxf4nvf4.block_scale (K = 64 each) per
-//             slab, accumulating into TMEM; tcgen05.commit releases the stage;
+//             slab, accumulating into TMEM; tcgen05.commit releases the stage (the decode variant
+//             has a second issuer, warp 19, with an accumulator of its own);
 //   * warps 2-9: scale warps - two sets of four (one warp per 32-lane quarter of tensor
 //             memory), each set owning the stages of one parity: ld.shared the slab's scale
 //             factors and tcgen05.st them into the stage's tensor-memory columns;
@@ -554,8 +557,12 @@ __global__ void __launch_bounds__(kThreads + 32 * (MMAS - 1), 1)
     }
   } else if (warp < kWarpEpi0) {
     // ================= scale warps: shared memory -> registers -> tensor memory =================
-    // tcgen05.cp would do this copy inside the tensor pipe, where every copy displaces an MMA for
-    // about as long as an MMA takes; going through registers keeps the pipe for the MMAs alone.
+    // tcgen05.cp would do this copy with one shared-memory read instead of four, but every tcgen05
+    // instruction costs the thread that issues it 35-70 cycles: the twelve copies of a slab plus their
+    // commit take a thread ~760 cycles, and that delay sits on the path from "scales landed" to "MMA may
+    // start".  Issued by the MMA thread the copies tripled its time per slab; issued by two threads of
+    // their own (stages by parity) the kernel was still 6 % slower than with these warps, whose path
+    // takes ~210 cycles (8192^3: 220.6 against 207.5 us; decode 13.8 against 11.8 us).
     // TMEM lane L, column 4*kb + j of a stage's scale area holds the four scales (one per 16-wide
     // K block of k-block kb) of tile row 32*j + L % 32, i.e. 16-byte row L % 32 of the 512-byte
     // swizzled block; every 32-lane quarter carries the same data.

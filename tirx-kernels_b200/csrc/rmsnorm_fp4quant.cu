@@ -343,8 +343,9 @@ __global__ void __launch_bounds__(128) rmsnorm_fp4quant_block_kernel(const __gri
   if (p.stagger_ns > 0 && static_cast<int>(blockIdx.x) < p.first_ctas) {
     const int slot = static_cast<int>(blockIdx.x) / p.sm_count;
     const unsigned long long wait_ns = slot < p.stagger_free ? 0ull : static_cast<unsigned long long>(slot - p.stagger_free + 1) * p.stagger_ns;
-    // a fixed number of short sleeps: bounded whatever a timer does under a profiler
-    for (unsigned long long slept = 0; slept < wait_ns; slept += 128) __nanosleep(128);
+    // timed by the global timer, and bounded by a count of short sleeps whatever that timer does
+    const unsigned long long t0 = global_timer_ns();
+    for (unsigned long long i = 0; i < wait_ns / 32 + 8 && global_timer_ns() - t0 < wait_ns; ++i) __nanosleep(64);
   }
   const float rcp6 = rcp_approx_ftz(6.0f);
   const uint8_t* xrow = p.x + static_cast<int64_t>(row) * p.H * 2;
