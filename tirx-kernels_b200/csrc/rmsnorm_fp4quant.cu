@@ -46,6 +46,7 @@ struct RmsParams {
   int first_ctas;     // CTAs resident at launch (they are the ones that get an offset)
   int sm_count;
   int stagger_free;   // CTAs per SM that start at once
+  int stagger_first;  // offset of the first delayed CTA of an SM (-1: same as stagger_ns)
   unsigned long long* timeline;  // block-owner kernel: per CTA {start, rows reduced, end} in ns and the SM id; null = off
 };
 
@@ -342,7 +343,8 @@ __global__ void __launch_bounds__(128) rmsnorm_fp4quant_block_kernel(const __gri
   // by themselves; the first ones are spread out here: the k-th CTA of an SM starts k * stagger_ns late.
   if (p.stagger_ns > 0 && static_cast<int>(blockIdx.x) < p.first_ctas) {
     const int slot = static_cast<int>(blockIdx.x) / p.sm_count;
-    const unsigned long long wait_ns = slot < p.stagger_free ? 0ull : static_cast<unsigned long long>(slot - p.stagger_free + 1) * p.stagger_ns;
+    unsigned long long wait_ns = slot < p.stagger_free ? 0ull : static_cast<unsigned long long>(slot - p.stagger_free + 1) * p.stagger_ns;
+    if (p.stagger_first >= 0 && slot >= p.stagger_free) wait_ns = p.stagger_first + static_cast<unsigned long long>(slot - p.stagger_free) * p.stagger_ns;
     // timed by the global timer, and bounded by a count of short sleeps whatever that timer does
     const unsigned long long t0 = global_timer_ns();
     for (unsigned long long i = 0; i < wait_ns / 32 + 8 && global_timer_ns() - t0 < wait_ns; ++i) __nanosleep(64);
@@ -665,16 +667,22 @@ int g_prefetch = [] {
   return v ? atoi(v) : -1;
 }();
 
-// Tuning knob: B2_RMSNORM_STAGGER_NS = start offset, in nanoseconds, between the CTAs that share an SM at
-// launch (block-owner kernel; 0 = all start together; default: 1500 for rows of 7 or 8 scale blocks per
-// thread, none otherwise).  Measured at 8192 x 7168 with cold inputs: the CTAs resident at launch all wait
-// ~6 us for their rows (888 CTAs ask for 25 MB at once), then all quantize for ~4 us with HBM idle; with the
-// k-th CTA of every SM starting 1.5 k us late the steady mix of loading and quantizing CTAs is reached 2 us
-// earlier: 31.5 -> 29.6 us (800 ns: 31.4, 1200: 30.4, 2000: 30.8; letting two or three CTAs per SM start at
-// once: no gain at any offset).  Rows of 4096 values lose 3 % with it.
+// Tuning knobs: B2_RMSNORM_STAGGER_FIRST_NS / B2_RMSNORM_STAGGER_NS = when the CTAs that share an SM at launch
+// start (block-owner kernel): the first at once, the second after FIRST ns, every further one NS ns later
+// (NS = 0: all start together; FIRST = -1: FIRST = NS).  Default for rows of 7 or 8 scale blocks per thread in
+// launches of two generations of CTAs or more: 3500 / 800, none otherwise.  Measured at 8192 x 7168 with cold
+// inputs: the CTAs resident at launch all wait ~6 us for their rows (888 CTAs ask for 25 MB at once), then all
+// quantize for ~4 us with HBM idle; spread out, the steady mix of loading and quantizing CTAs is reached
+// earlier: 31.5 us with no offsets; a uniform offset of 800 ns 31.4, 1200 30.4, 1500 29.5, 2000 30.8; first
+// 2500-3500 then 800-1000: 29.1-29.3 (letting two or three CTAs per SM start at once: no gain at any offset).
+// Rows of 4096 values lose 3 % with it.
 int g_stagger_ns = [] {
   const char* v = getenv("B2_RMSNORM_STAGGER_NS");
   return v ? atoi(v) : -1;
+}();
+int g_stagger_first_ns = [] {
+  const char* v = getenv("B2_RMSNORM_STAGGER_FIRST_NS");
+  return v ? atoi(v) : -2;  // -2: default
 }();
 
 // Device buffer of the per-CTA timeline (b2_rmsnorm_fp4quant_timeline); null = not recording.
@@ -717,9 +725,10 @@ int launch_block_owner(Kernel kernel, RmsParams p, int rows_per_cta, cudaStream_
   // (only where at least two generations of CTAs follow one another: a launch that fits the GPU at once
   // would merely start late)
   const int grid = (p.M + rows_per_cta - 1) / rows_per_cta;
-  p.stagger_ns = g_stagger_ns < 0 ? (long_rows && grid >= 2 * resident ? 1500 : 0) : g_stagger_ns;
+  p.stagger_ns = g_stagger_ns < 0 ? (long_rows && grid >= 2 * resident ? 800 : 0) : g_stagger_ns;
   p.first_ctas = resident;
   p.stagger_free = g_stagger_free;
+  p.stagger_first = g_stagger_first_ns < -1 ? (p.stagger_ns > 0 && g_stagger_ns < 0 ? 3500 : -1) : g_stagger_first_ns;
   p.timeline = g_timeline.load(std::memory_order_relaxed);
   p.sm_count = std::max(device_sm_count(), 1);
   return launch_config(kernel, p, rows_per_cta, 128, 0, stream);
@@ -854,6 +863,7 @@ extern "C" int b2_rmsnorm_fp4quant(const void* x, const void* w, void* y, void* 
   p.first_ctas = 0;
   p.sm_count = 1;
   p.stagger_free = 1;
+  p.stagger_first = -1;
   p.timeline = nullptr;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int cluster_n = source_cluster_n(H);
