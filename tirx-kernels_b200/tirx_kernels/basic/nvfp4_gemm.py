@@ -221,9 +221,36 @@ def run_gpu(prepared, *, warmup=None, repeat=None, timer=None, **kwargs):
         metadata["cublaslt_vs_tir_rel_fro"] = relative_frobenius_error(out_tir, out_lt)
         return launch
 
+    def _flashinfer():
+        """flashinfer's `mm_fp4`, the reference's second timing peer (tirx_kernels/basic/nvfp4_gemm.py:1153-1222):
+        the same packed operands and swizzled scales, tuned once for this shape before it is timed.  The
+        back-end is the one the reference reports (cuDNN) unless B2_FLASHINFER_MM_FP4_BACKEND names another."""
+        import os
+
+        import flashinfer
+
+        backend = os.environ.get("B2_FLASHINFER_MM_FP4_BACKEND", "cudnn")
+        out_fi = torch.empty_like(out_tir)
+        pad = lambda rows: _checks.ceil_div(rows, 128) * 128
+        a_sf = A_sf.view(pad(M), K // 16)
+        b_sf = B_sf.view(pad(N), K // 16)
+
+        def launch():
+            flashinfer.mm_fp4(A_fp4, B_fp4.T, a_sf, b_sf.T, alpha_tensor, out=out_fi, block_size=16, backend=backend,
+                              use_nvfp4=True)
+
+        with flashinfer.autotune(True):
+            launch()
+        torch.cuda.synchronize()
+        funcs["tir"]()
+        torch.cuda.synchronize()
+        metadata["flashinfer_mm_fp4_backend"] = backend
+        metadata["flashinfer_mm_fp4_vs_tir_rel_fro"] = relative_frobenius_error(out_tir, out_fi)
+        return launch
+
     protocol = {k: config.pop(k) for k in ("rounds", "cooldown_s") if k in config}
-    result = bench(funcs, warmup=warmup, repeat=repeat, timer=timer, references={"cublaslt_nvfp4": _cublaslt},
-                   **protocol)
+    result = bench(funcs, warmup=warmup, repeat=repeat, timer=timer,
+                   references={"cublaslt_nvfp4": _cublaslt, "flashinfer_mm_fp4": _flashinfer}, **protocol)
     _native.nvfp4_gemm_status()
     microseconds = result["impls"]["tir"]
     if M >= 1024:
