@@ -79,6 +79,6 @@ def test_rejects_what_does_not_fit_the_built_in_scratch(native):
     d = torch.empty(1 << 20, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(ValueError, match="1 <= M <= 128"):
         native.nvfp4_gemm_small_m_noalloc(z, z, z, z, one, d, 256, 1024, 1024)
-    # 128 x 2048 in 8 K ranges would need 8 MiB of partial sums
+    # 128 x 4608 is 72 tiles of 64 columns; cut into two K ranges (144 CTAs) it would need 4.5 MiB of partial sums
     with pytest.raises(ValueError, match="built-in scratch"):
-        native.nvfp4_gemm_small_m_noalloc(z, z, z, z, one, d, 128, 2048, 16384)
+        native.nvfp4_gemm_small_m_noalloc(z, z, z, z, one, d, 128, 4608, 2048)

@@ -1166,6 +1166,9 @@ int choose_variant(int M, int N, int K) {
     // M <= 32 and no more 64-wide tiles than SMs: every CTA takes one tile and all of K, two warps issue
     // its MMAs; no K ranges, no second kernel (16 x 8192 x 8192: 11.8 us against 13.1 with K ranges).
     if (sms > 0 && M <= 32 && N / 64 <= sms && K >= 512) return 7;
+    // The same tiling with all 128 rows of A per stage for 32 < M <= 128 (128 x 8192 x 8192: 12.5 us against
+    // 16.1 with 128-wide tiles and K ranges; 64 x 8192 x 8192: 12.2 against 14.5).
+    if (sms > 0 && N / 64 <= sms && K >= 512) return 8;
     int variant = 0;
     if (sms > 0 && M <= 32 && N % 256 == 0) {
       const int k_slabs = K / kBlockK;
@@ -1194,10 +1197,10 @@ int choose_variant(int M, int N, int K) {
 // Selects a kernel variant for the following calls of this process (-1 restores automatic
 // selection).  0: single CTA, N tile 128; 1: single CTA, N tile 256; 2: CTA pair, N tile 256;
 // 3: CTA pair, N tile 128; 4 and 5: 0 and 1 for M <= 32, loading 32 rows of A per stage into a deeper
-// ring; 6: M <= 32, N tile 64; 7: 6 with two MMA-issuing warps.  Used by the tests to exercise every variant
-// on small shapes.
+// ring; 6: M <= 32, N tile 64; 7: 6 with two MMA-issuing warps; 8: 7 with all 128 rows of A per stage
+// (M <= 128).  Used by the tests to exercise every variant on small shapes.
 extern "C" int b2_nvfp4_gemm_set_variant(int variant) {
-  if (variant < -1 || variant > 7) {
+  if (variant < -1 || variant > 8) {
     b2::set_error("b2_nvfp4_gemm_set_variant: unknown variant %d", variant);
     return B2_ERR_INVALID_ARGUMENT;
   }
@@ -1231,6 +1234,10 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
   int variant = g_forced_variant.load(std::memory_order_relaxed);
   if (variant < 0) variant = choose_variant(M, N, K);
   if (variant == 7 && K < 512) variant = 6;  // the second MMA warp needs a K slab of its own
+  if (variant == 8 && (K < 512 || M > 128)) {
+    set_error("b2_nvfp4_gemm: variant 8 needs M <= 128 and K >= 512");
+    return B2_ERR_INVALID_ARGUMENT;
+  }
   if ((variant == 4 || variant == 5 || variant == 6 || variant == 7) && M > 32) {
     set_error("b2_nvfp4_gemm: variant %d needs M <= 32", variant);
     return B2_ERR_INVALID_ARGUMENT;
@@ -1247,6 +1254,7 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
     case 5: return launch_variant<1, 256, 5, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 5, s);
     case 6: return launch_variant<1, 64, 13, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 6, s);
     case 7: return launch_variant<1, 64, 11, 0, 32, 2>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 7, s);
+    case 8: return launch_variant<1, 64, 7, 0, 128, 2>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 8, s);
     default: return launch_variant<2, 128, 6, 1>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
   }
 }
@@ -1390,6 +1398,7 @@ extern "C" int b2_nvfp4_gemm_small_m_noalloc(const void* A, const void* B, const
     case 1: return launch_variant<1, 256, 4>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 1, s, &ws);
     case 4: return launch_variant<1, 128, 9, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 4, s, &ws);
     case 7: return launch_variant<1, 64, 11, 0, 32, 2>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 7, s, &ws);
+    case 8: return launch_variant<1, 64, 7, 0, 128, 2>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 8, s, &ws);
     default: return launch_variant<1, 256, 5, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 5, s, &ws);
   }
 }
