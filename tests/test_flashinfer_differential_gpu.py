@@ -127,3 +127,51 @@ def test_gemm_operand_bytes_equal_flashinfer(native):
         want_packed, want_sf, _ = _flashinfer_quantize(origin, gs, "128x4")
         _assert_same_bytes(packed, want_packed, f"{name}: packed E2M1")
         _assert_same_bytes(sf, want_sf, f"{name}: swizzled scales")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_silu_fused_quantizer_against_flashinfer_composition(dtype, native):
+    """The SiLU-fused quantizer has no fused counterpart in the flashinfer build beside this package (the
+    reference compares with `silu_and_mul_nvfp4_quantize`, nvfp4_quantize.py:418-438).  What that build does
+    have is the composition the fused kernel is defined to equal: `silu_and_mul` (gate|up -> the input
+    dtype) followed by `nvfp4_quantize`.  Two comparisons: this package's plain quantizer on flashinfer's
+    SiLU output must equal flashinfer's quantizer byte for byte (the quantizer stage alone), and the fused
+    kernel must agree with the composition up to the rare element where the two SiLU implementations round
+    an fp32 intermediate differently (each such element can move one packed byte by one E2M1 step or, at a
+    block maximum, one scale byte): the differing count is printed and bounded.  Measured on a B200: bf16
+    0 of 7,340,032 packed bytes and 0 of 917,504 scale bytes; fp16 2 packed bytes and 0 scale bytes."""
+    _flashinfer()
+    try:
+        from flashinfer.activation import silu_and_mul
+    except Exception as error:
+        pytest.skip(f"flashinfer.activation.silu_and_mul is not importable here: {type(error).__name__}: {error}")
+    m, k, layout = 4096, 3584, "128x4"
+    name = {torch.bfloat16: "bfloat16", torch.float16: "float16"}[dtype]
+    g = torch.Generator().manual_seed(42)
+    x = torch.randn(m, 2 * k, generator=g, dtype=torch.float32).to(dtype).cuda()
+    gs = torch.tensor([1.25], device="cuda")
+    try:
+        activated = silu_and_mul(x)
+        torch.cuda.synchronize()
+    except Exception as error:
+        pytest.skip(f"flashinfer could not build or run silu_and_mul here: {type(error).__name__}: {str(error)[:200]}")
+    want_packed, want_sf, backend = _flashinfer_quantize(activated, gs, layout)
+    sf_bytes = native.lib().b2_nvfp4_sf_bytes(m, k, native.SF_LAYOUT_CODES[layout])
+    # stage 2 alone: the plain quantizer on flashinfer's activated tensor
+    out = torch.empty(m, k // 2, dtype=torch.uint8, device="cuda")
+    sf = torch.empty(sf_bytes, dtype=torch.uint8, device="cuda")
+    native.nvfp4_quantize(activated.contiguous(), out, sf, gs, m, k, name, layout)
+    torch.cuda.synchronize()
+    _assert_same_bytes(out, want_packed, "quantizer stage: packed E2M1")
+    _assert_same_bytes(sf, want_sf, "quantizer stage: scale buffer")
+    # the fused kernel against the composition
+    fused_out = torch.empty_like(out)
+    fused_sf = torch.empty_like(sf)
+    native.nvfp4_quantize(x, fused_out, fused_sf, gs, m, k, name, layout, fuse_silu=True)
+    torch.cuda.synchronize()
+    packed_diff = int((fused_out.reshape(-1) != want_packed.reshape(-1)).sum())
+    sf_diff = int((fused_sf.reshape(-1) != want_sf.reshape(-1)).sum())
+    print(f"{name}: {packed_diff} of {fused_out.numel()} packed bytes and {sf_diff} of {fused_sf.numel()} scale bytes "
+          f"differ from silu_and_mul + nvfp4_quantize ({backend})")
+    assert packed_diff <= fused_out.numel() * 1e-5
+    assert sf_diff <= fused_sf.numel() * 1e-5
