@@ -34,6 +34,7 @@
 #include <cuda.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -456,9 +457,15 @@ __global__ void __launch_bounds__(kThreads + 32 * (MMAS - 1), 1)
   if constexpr (CG == 2) cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // With K ranges a second kernel adds the partial sums: let it launch now and wait, resident, for this
-  // grid to finish, instead of paying its launch after the last CTA has left.
-  if (p.splits > 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // Programmatic dependent launch, both ways.  This grid may have been launched before its predecessor on
+  // the stream finished: everything above touched only this CTA's own shared and tensor memory, and nothing
+  // below reads or writes global memory before the predecessor has completed and its writes are visible.
+  // Then let the next launch start: with K ranges that is the kernel that adds the partial sums (resident
+  // beside this grid, waiting), otherwise it is whatever follows with the same launch attribute - another
+  // GEMM of a decode step is scheduled onto every SM the moment this grid's CTA leaves it, instead of after
+  // the whole grid has drained and a launch has been processed.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == kWarpProducer) {
     // ================= TMA producer =================
@@ -882,6 +889,12 @@ constexpr int kStatusWords = 64;  // 2 status words, padding, 12 64-bit role tim
 std::atomic<int> g_profile{0};
 std::atomic<unsigned long long> g_wait_budget_ns{kWaitBudgetNs};
 std::atomic<int> g_test_fault{0};  // consumed by the next launch
+// Launch the GEMM with the programmatic-dependent-launch attribute (B2_GEMM_PDL=0 turns it off).
+int pdl_from_env() {
+  const char* v = std::getenv("B2_GEMM_PDL");
+  return (v && v[0] == '0') ? 0 : 1;
+}
+std::atomic<int> g_pdl{pdl_from_env()};
 
 
 // Device status word of the current device, allocated (and zeroed) on first use.
@@ -1019,6 +1032,12 @@ int launch_kernels(const MapSet& maps, const float* alpha, void* D, int M, int N
     attr[cfg.numAttrs].val.clusterDim.x = 2;
     attr[cfg.numAttrs].val.clusterDim.y = 1;
     attr[cfg.numAttrs].val.clusterDim.z = 1;
+    ++cfg.numAttrs;
+  }
+  if (g_pdl.load(std::memory_order_relaxed)) {
+    // May start while the previous kernel on the stream is still running; see griddepcontrol.wait in the kernel.
+    attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
     ++cfg.numAttrs;
   }
   B2_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps.a, maps.b, maps.sfa, maps.sfb, p, out_maps));
