@@ -160,6 +160,14 @@ int b2_add_rmsnorm_fp4quant(const void* x, void* residual, const void* w, void* 
  * that allocates inside a capture invalidates it); calls on one device share the scratch, so keep
  * them in stream order - two such calls that overlap on the GPU (different streams, graphs
  * replayed concurrently) race on it.
+ *
+ * Launch order: the kernel is launched with the programmatic-stream-serialization attribute.  It may
+ * therefore become resident while the kernel before it on `stream` is still running, but it executes
+ * griddepcontrol.wait before its first access to global memory, so it observes everything earlier
+ * work on the stream wrote, as an ordinary launch does; it then executes
+ * griddepcontrol.launch_dependents, which matters only to a following kernel that was itself
+ * launched with that attribute (such a kernel must wait the same way before it reads D).
+ * B2_GEMM_PDL=0 in the environment launches without the attribute.
  */
 int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, const void* SFB,
                   const float* alpha_dev, void* D, int M, int N, int K, void* stream);
