@@ -176,7 +176,8 @@ int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, const void* SFB
  * (-1 restores automatic selection): 0 single CTA / N tile 128, 1 single CTA / N tile 256,
  * 2 CTA pair / N tile 256, 3 CTA pair / N tile 128, 4 and 5 = 0 and 1 for M <= 32 (32 rows of A
  * per stage, deeper ring), 6 = M <= 32 with N tile 64 and all of K per CTA, 7 = 6 with two MMA-issuing
- * warps (two accumulators, added in the epilogue), 8 = 7 with 128 rows of A per stage (M <= 128).  The reference fixes its tiling per
+ * warps (two accumulators, added in the epilogue), 8 = 7 with 128 rows of A per stage (M <= 128), 9 = 0 with two
+ * MMA-issuing warps (chosen for M > 128 when the 128 x 128 tiles fit the SMs in one wave).  The reference fixes its tiling per
  * shape in TIRX_CONFIGS, tirx_kernels/basic/nvfp4_gemm.py:860-903; this is the matching knob. */
 int b2_nvfp4_gemm_set_variant(int variant);
 

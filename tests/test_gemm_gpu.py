@@ -25,7 +25,7 @@ SMALL_SHAPES = [(128, 128, 256), (256, 256, 256), (384, 640, 768), (1024, 1024, 
                 (200, 384, 512), (1, 256, 4096), (32, 1024, 8192), (7, 768, 2304)]
 
 
-@pytest.mark.parametrize("which", [0, 1, 2, 3, 4, 5, 6, 7, 8])
+@pytest.mark.parametrize("which", [0, 1, 2, 3, 4, 5, 6, 7, 8, 9])
 @pytest.mark.parametrize("M,N,K", SMALL_SHAPES)
 def test_every_variant_matches_the_oracle(which, M, N, K, variant, native):
     import oracle_provider

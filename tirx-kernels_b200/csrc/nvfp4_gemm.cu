@@ -1201,6 +1201,10 @@ int choose_variant(int M, int N, int K) {
     if (M <= 32) variant += 4;  // 32 rows of A per stage, deeper ring
     return variant;
   }
+  // At most one 128 x 128 tile per SM: single-CTA tiles in one wave, two warps issuing alternate K slabs into
+  // two accumulators (256 x 8192 x 8192: 14.3 us against 15.9 with 256 x 128 pair tiles, 512 x 4096 x 4096:
+  // 9.3 against 10.5; cold weights, launches in a CUDA graph).
+  if (sms > 0 && static_cast<int64_t>((M + 127) / 128) * (N / 128) <= sms && K >= 512) return 9;
   int variant = N % 256 == 0 ? 2 : 3;
   if (variant == 2) {
     // few 256 x 256 tiles (fewer than half the CTA pairs busy): 256 x 128 tiles double the parallelism
@@ -1217,9 +1221,9 @@ int choose_variant(int M, int N, int K) {
 // selection).  0: single CTA, N tile 128; 1: single CTA, N tile 256; 2: CTA pair, N tile 256;
 // 3: CTA pair, N tile 128; 4 and 5: 0 and 1 for M <= 32, loading 32 rows of A per stage into a deeper
 // ring; 6: M <= 32, N tile 64; 7: 6 with two MMA-issuing warps; 8: 7 with all 128 rows of A per stage
-// (M <= 128).  Used by the tests to exercise every variant on small shapes.
+// (M <= 128); 9: 0 with two MMA-issuing warps.  Used by the tests to exercise every variant on small shapes.
 extern "C" int b2_nvfp4_gemm_set_variant(int variant) {
-  if (variant < -1 || variant > 8) {
+  if (variant < -1 || variant > 9) {
     b2::set_error("b2_nvfp4_gemm_set_variant: unknown variant %d", variant);
     return B2_ERR_INVALID_ARGUMENT;
   }
@@ -1253,6 +1257,7 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
   int variant = g_forced_variant.load(std::memory_order_relaxed);
   if (variant < 0) variant = choose_variant(M, N, K);
   if (variant == 7 && K < 512) variant = 6;  // the second MMA warp needs a K slab of its own
+  if (variant == 9 && K < 512) variant = 0;
   if (variant == 8 && (K < 512 || M > 128)) {
     set_error("b2_nvfp4_gemm: variant 8 needs M <= 128 and K >= 512");
     return B2_ERR_INVALID_ARGUMENT;
@@ -1274,6 +1279,7 @@ extern "C" int b2_nvfp4_gemm(const void* A, const void* B, const void* SFA, cons
     case 6: return launch_variant<1, 64, 13, 0, 32>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 6, s);
     case 7: return launch_variant<1, 64, 11, 0, 32, 2>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 7, s);
     case 8: return launch_variant<1, 64, 7, 0, 128, 2>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 8, s);
+    case 9: return launch_variant<1, 128, 6, 0, 128, 2>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 9, s);
     default: return launch_variant<2, 128, 6, 1>(A, B, SFA, SFB, alpha_dev, D, M, N, K, 3, s);
   }
 }
