@@ -234,6 +234,62 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
       "h"(static_cast<uint16_t>(3))
       : "memory");
 }
+// One K slab from the issuing thread's side: the four MMAs and the commit that hands the stage back, with the
+// poll of the barrier the thread needs NEXT issued in front of them and its result read behind them.  A poll
+// takes the thread 100-200 cycles even when the barrier completed long ago (by the time the MMA thread reaches
+// a stage its operands and scales have been there for ~2000 cycles), and in one instruction stream that wait
+// was serial with the ~50 cycles per MMA: the thread, not the ring or the tensor pipe, set the time per slab.
+// Returns whether the next barrier's phase had completed.
+template <int CG>
+__device__ __forceinline__ uint32_t tc_slab_and_poll_next(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                         uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                                         uint32_t sfb_step, uint32_t accumulate_first,
+                                                         uint32_t commit_bar, uint32_t next_bar,
+                                                         uint32_t next_parity) {
+  uint32_t ok;
+#define B2_MMA_(cg, d, a, b, sa, sb, pr) \
+  "tcgen05.mma.cta_group::" cg ".kind::mxf4nvf4.block_scale.scale_vec::4X [" d "], " a ", " b ", %10, [" sa "], [" sb "], " pr ";\n"
+  if constexpr (CG == 1) {
+    asm volatile(
+        "{ .reg .pred p, q, t;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 q, [%21], %22;\n"
+        "setp.ne.b32 p, %19, 0;\n"
+        "setp.eq.b32 t, %10, %10;\n"
+        B2_MMA_("1", "%1", "%2", "%6", "%11", "%15", "p")
+        B2_MMA_("1", "%1", "%3", "%7", "%12", "%16", "t")
+        B2_MMA_("1", "%1", "%4", "%8", "%13", "%17", "t")
+        B2_MMA_("1", "%1", "%5", "%9", "%14", "%18", "t")
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%20];\n"
+        "selp.u32 %0, 1, 0, q; }"
+        : "=r"(ok)
+        : "r"(d_tmem), "l"(a_desc), "l"(a_desc + 2), "l"(a_desc + 4), "l"(a_desc + 6), "l"(b_desc),
+          "l"(b_desc + 2), "l"(b_desc + 4), "l"(b_desc + 6), "r"(idesc), "r"(sfa), "r"(sfa + 4), "r"(sfa + 8),
+          "r"(sfa + 12), "r"(sfb), "r"(sfb + sfb_step), "r"(sfb + 2 * sfb_step), "r"(sfb + 3 * sfb_step),
+          "r"(accumulate_first), "r"(commit_bar), "r"(next_bar), "r"(next_parity)
+        : "memory");
+  } else {
+    asm volatile(
+        "{ .reg .pred p, q, t;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 q, [%21], %22;\n"
+        "setp.ne.b32 p, %19, 0;\n"
+        "setp.eq.b32 t, %10, %10;\n"
+        B2_MMA_("2", "%1", "%2", "%6", "%11", "%15", "p")
+        B2_MMA_("2", "%1", "%3", "%7", "%12", "%16", "t")
+        B2_MMA_("2", "%1", "%4", "%8", "%13", "%17", "t")
+        B2_MMA_("2", "%1", "%5", "%9", "%14", "%18", "t")
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%20], %23;\n"
+        "selp.u32 %0, 1, 0, q; }"
+        : "=r"(ok)
+        : "r"(d_tmem), "l"(a_desc), "l"(a_desc + 2), "l"(a_desc + 4), "l"(a_desc + 6), "l"(b_desc),
+          "l"(b_desc + 2), "l"(b_desc + 4), "l"(b_desc + 6), "r"(idesc), "r"(sfa), "r"(sfa + 4), "r"(sfa + 8),
+          "r"(sfa + 12), "r"(sfb), "r"(sfb + sfb_step), "r"(sfb + 2 * sfb_step), "r"(sfb + 3 * sfb_step),
+          "r"(accumulate_first), "r"(commit_bar), "r"(next_bar), "r"(next_parity),
+          "h"(static_cast<uint16_t>(3))
+        : "memory");
+  }
+#undef B2_MMA_
+  return ok;
+}
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -526,27 +582,35 @@ __global__ void __launch_bounds__(kThreads + 32 * (MMAS - 1), 1)
           tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
           sfb_half = static_cast<uint32_t>(tn & 1) * 2u;
         }
+        // ring position of this issuer's first slab of the tile; from there it moves MMAS stages per slab
+        int stage = (slab0 + me) % STAGES;
+        uint32_t phase = static_cast<uint32_t>((slab0 + me) / STAGES) & 1u;
+        bool polled = false;  // the poll issued with the previous slab already found this slab's barrier complete
         for (int ks = me; ks < k_slabs; ks += MMAS) {
-          const int n = slab0 + ks;
-          const int stage = n % STAGES;
-          const uint32_t phase = static_cast<uint32_t>(n / STAGES) & 1u;
           const long long w0 = mprof ? clock64() : 0;
-          if (!wait_or_abort<kClusterAcquireWaits && CG == 2>(full_bar(stage), phase, ctx, 3u)) { alive = false; break; }
+          if (!polled && !wait_or_abort<kClusterAcquireWaits && CG == 2>(full_bar(stage), phase, ctx, 3u)) {
+            alive = false;
+            break;
+          }
           const long long w1 = mprof ? clock64() : 0;
           t_full += w1 - w0;
           tc_fence_after();
           const uint32_t sbase = smem_base + stage * L::kStageBytes;
           const uint32_t sf_tmem = tmem_base + kAccCols + stage * L::kSfCols;
-          const uint64_t a_desc = operand_desc(sbase);
-          const uint64_t b_desc = operand_desc(sbase + L::kABytes);
-#pragma unroll
-          for (int kb = 0; kb < 4; ++kb) {
-            // 64 fp4 values = 32 bytes = 2 descriptor address units inside the swizzled row
-            tc_mma<CG>(acc_tmem, a_desc + 2 * kb, b_desc + 2 * kb, kIdesc, sf_tmem + kb * 4,
-                       sf_tmem + 16 + kb * 4 * L::kChunks + sfb_half, (ks >= MMAS || kb) ? 1u : 0u);
-          }
-          if constexpr (CG == 2) tc_commit_pair(empty_bar(stage));
-          else tc_commit<CG>(empty_bar(stage));
+          int next_stage = stage + MMAS;
+          uint32_t next_phase = phase;
+          if (next_stage >= STAGES) { next_stage -= STAGES; next_phase ^= 1u; }
+          const bool more = ks + MMAS < k_slabs;
+          // 64 fp4 values = 32 bytes = 2 descriptor address units inside the swizzled row: the helper steps the
+          // descriptors by 2, the scales of A by 4 columns and those of B by 4 per 128-row chunk per MMA.
+          // After the tile's last slab there is nothing to poll: it polls this slab's own, completed barrier.
+          const uint32_t ok = tc_slab_and_poll_next<CG>(
+              acc_tmem, operand_desc(sbase), operand_desc(sbase + L::kABytes), kIdesc, sf_tmem,
+              sf_tmem + 16 + sfb_half, 4 * L::kChunks, ks >= MMAS ? 1u : 0u, empty_bar(stage),
+              full_bar(more ? next_stage : stage), more ? next_phase : phase);
+          polled = more && ok != 0;
+          stage = next_stage;
+          phase = next_phase;
           if (mprof) t_issue += clock64() - w1;
         }
         if (!alive) break;
