@@ -234,6 +234,12 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
       "h"(static_cast<uint16_t>(3))
       : "memory");
 }
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{ .reg .pred P; elect.sync _|P, 0xffffffff; selp.u32 %0, 1, 0, P; }" : "=r"(pred));
+  return pred != 0;
+}
 // One K slab from the issuing thread's side: the four MMAs and the commit that hands the stage back, with the
 // poll of the barrier the thread needs NEXT issued in front of them and its result read behind them.  A poll
 // takes the thread 100-200 cycles even when the barrier completed long ago (by the time the MMA thread reaches
@@ -478,9 +484,13 @@ __global__ void __launch_bounds__(kThreads + 32 * (MMAS - 1), 1)
   volatile uint32_t* abort_flag = tmem_slot + 1;
   const WaitCtx ctx{p.status, abort_flag, p.wait_budget_ns};
 
-  const int warp = threadIdx.x >> 5;
+  // Broadcast from lane 0: the value is the same in every lane anyway, but this way the compiler knows it, keeps
+  // the role dispatch and everything computed from these in uniform registers and uniform control flow.
+  constexpr bool kWarpWide = CG == 2;  // see the issuing roles below
+  const int warp = kWarpWide ? __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0)
+                             : static_cast<int>(threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;
+  const uint32_t rank = CG == 2 ? __shfl_sync(0xffffffffu, cluster_ctarank(), 0) : 0u;
   const bool leader = rank == 0;
   const int unit = CG == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int num_units = CG == 2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
@@ -512,7 +522,7 @@ __global__ void __launch_bounds__(kThreads + 32 * (MMAS - 1), 1)
   __syncthreads();
   if constexpr (CG == 2) cluster_sync_all();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = kWarpWide ? __shfl_sync(0xffffffffu, *tmem_slot, 0) : *tmem_slot;
   // Programmatic dependent launch, both ways.  This grid may have been launched before its predecessor on
   // the stream finished: everything above touched only this CTA's own shared and tensor memory, and nothing
   // below reads or writes global memory before the predecessor has completed and its writes are visible.
@@ -523,107 +533,230 @@ __global__ void __launch_bounds__(kThreads + 32 * (MMAS - 1), 1)
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
+  // The three issuing roles (operand copies, scale copies, MMAs) are, in the CTA-pair kernels, loops that the WHOLE warp runs,
+  // with one elected lane issuing (kWarpWide).  TMA and tcgen05 instructions take their operands from uniform registers; what every
+  // lane of a converged warp computes alike (ring position, barrier and shared-memory addresses, descriptors)
+  // the compiler can keep there, whereas in a loop that only lane 0 runs every operand of every such
+  // instruction is moved there first.  All lanes wait on the barriers (also the fastest way to be woken: a
+  // lane waiting for its warp and handing the result on by shuffle takes twice as long) and agree on the
+  // outcome by a vote, so the warp leaves the loop together when a wait gives up.
   if (warp == kWarpProducer) {
-    // ================= TMA producer =================
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool alive = true;
-      uint32_t excess_tx = (p.test_fault == 1 && blockIdx.x == 0) ? 16u : 0u;  // test hook, see GemmParams
-      long long t_wait = 0, t_begin = prof ? clock64() : 0;
-      for (int t = unit; t < num_tiles && alive; t += num_units) {
-        int tm, tn;
-        tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
-        const int row_a = (tm * CG + static_cast<int>(rank)) * kBlockM;
-        const int row_b = tn * BN + static_cast<int>(rank) * L::kBRows;
-        const int k_first = (t % p.splits) * k_slabs;
-        for (int ks = k_first; ks < k_first + k_slabs; ++ks) {
-          const long long w0 = prof ? clock64() : 0;
-          if (!wait_or_abort(empty_bar(stage), phase ^ 1u, ctx, 1u)) { alive = false; break; }
-          if (prof) t_wait += clock64() - w0;
-          const uint32_t sbase = smem_base + stage * L::kStageBytes;
-          // operand bytes of both CTAs of a pair are counted on the leader's barrier
-          const uint32_t op_bar = CG == 2 ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
-          if (leader) mbar_expect_tx(full_bar(stage), kOperandTx + excess_tx);
-          excess_tx = 0;
-          tma_load_2d<CG>(sbase, &map_a, ks * 128, row_a, op_bar);
-          tma_load_2d<CG>(sbase + L::kABytes, &map_b, ks * 128, row_b, op_bar);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+    if constexpr (kWarpWide) {
+      // ================= TMA producer =================
+      {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        uint32_t excess_tx = (p.test_fault == 1 && blockIdx.x == 0) ? 16u : 0u;  // test hook, see GemmParams
+        long long t_wait = 0, t_begin = prof ? clock64() : 0;
+        for (int t = unit; t < num_tiles && alive; t += num_units) {
+          int tm, tn;
+          tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
+          const int row_a = (tm * CG + static_cast<int>(rank)) * kBlockM;
+          const int row_b = tn * BN + static_cast<int>(rank) * L::kBRows;
+          const int k_first = (t % p.splits) * k_slabs;
+          for (int ks = k_first; ks < k_first + k_slabs; ++ks) {
+            const long long w0 = prof ? clock64() : 0;
+            if (!__all_sync(0xffffffffu, wait_or_abort(empty_bar(stage), phase ^ 1u, ctx, 1u))) { alive = false; break; }
+            if (prof) t_wait += clock64() - w0;
+            const uint32_t sbase = smem_base + stage * L::kStageBytes;
+            // operand bytes of both CTAs of a pair are counted on the leader's barrier
+            const uint32_t op_bar = CG == 2 ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
+            if (elect_one()) {
+              if (leader) mbar_expect_tx(full_bar(stage), kOperandTx + excess_tx);
+              tma_load_2d<CG>(sbase, &map_a, ks * 128, row_a, op_bar);
+              tma_load_2d<CG>(sbase + L::kABytes, &map_b, ks * 128, row_b, op_bar);
+            }
+            __syncwarp();
+            excess_tx = 0;
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+        if (prof) {
+          counters[0] = t_wait;
+          counters[1] = clock64() - t_begin;
         }
       }
-      if (prof) {
-        counters[0] = t_wait;
-        counters[1] = clock64() - t_begin;
+    } else {
+      // ================= TMA producer =================
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        uint32_t excess_tx = (p.test_fault == 1 && blockIdx.x == 0) ? 16u : 0u;  // test hook, see GemmParams
+        long long t_wait = 0, t_begin = prof ? clock64() : 0;
+        for (int t = unit; t < num_tiles && alive; t += num_units) {
+          int tm, tn;
+          tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
+          const int row_a = (tm * CG + static_cast<int>(rank)) * kBlockM;
+          const int row_b = tn * BN + static_cast<int>(rank) * L::kBRows;
+          const int k_first = (t % p.splits) * k_slabs;
+          for (int ks = k_first; ks < k_first + k_slabs; ++ks) {
+            const long long w0 = prof ? clock64() : 0;
+            if (!wait_or_abort(empty_bar(stage), phase ^ 1u, ctx, 1u)) { alive = false; break; }
+            if (prof) t_wait += clock64() - w0;
+            const uint32_t sbase = smem_base + stage * L::kStageBytes;
+            // operand bytes of both CTAs of a pair are counted on the leader's barrier
+            const uint32_t op_bar = CG == 2 ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
+            if (leader) mbar_expect_tx(full_bar(stage), kOperandTx + excess_tx);
+            excess_tx = 0;
+            tma_load_2d<CG>(sbase, &map_a, ks * 128, row_a, op_bar);
+            tma_load_2d<CG>(sbase + L::kABytes, &map_b, ks * 128, row_b, op_bar);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+        if (prof) {
+          counters[0] = t_wait;
+          counters[1] = clock64() - t_begin;
+        }
       }
     }
   } else if (warp == kWarpMma || (MMAS == 2 && warp == kWarpMma2)) {
-    // ================= MMA issuer(s) (leader CTA only) =================
-    // Issuer `me` of MMAS takes the K slabs with (slab index in the tile) % MMAS == me and accumulates them
-    // in its own tensor-memory columns.
-    const int me = warp == kWarpMma ? 0 : 1;
-    if (leader && lane == 0) {
-      uint32_t acc_phase = 0;
-      bool alive = true;
-      int slab0 = 0;  // slabs of the tiles this CTA has finished: the ring position of the tile's first slab
-      const bool mprof = prof && me == 0;
-      long long t_full = 0, t_acc = 0, t_issue = 0, t_begin = mprof ? clock64() : 0;
-      const uint64_t ns_begin = mprof ? globaltimer_ns() : 0;
-      const uint32_t acc_tmem = tmem_base + static_cast<uint32_t>(me * BN);
-      for (int t = unit; t < num_tiles && alive; t += num_units, slab0 += k_slabs) {
-        const long long a0 = mprof ? clock64() : 0;
-        if (!wait_or_abort<kClusterAcquireWaits && CG == 2>(tmem_empty_bar, acc_phase ^ 1u, ctx, 2u)) break;
-        if (mprof) t_acc += clock64() - a0;
-        tc_fence_after();
-        // A 64-wide tile uses half of a 128-row scale chunk of B: the MMA reads N / 32 scale columns from
-        // the address it is given, so the upper half starts two columns in.
-        uint32_t sfb_half = 0;
-        if constexpr (BN == 64) {
-          int tm, tn;
-          tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
-          sfb_half = static_cast<uint32_t>(tn & 1) * 2u;
-        }
-        // ring position of this issuer's first slab of the tile; from there it moves MMAS stages per slab
-        int stage = (slab0 + me) % STAGES;
-        uint32_t phase = static_cast<uint32_t>((slab0 + me) / STAGES) & 1u;
-        bool polled = false;  // the poll issued with the previous slab already found this slab's barrier complete
-        for (int ks = me; ks < k_slabs; ks += MMAS) {
-          const long long w0 = mprof ? clock64() : 0;
-          if (!polled && !wait_or_abort<kClusterAcquireWaits && CG == 2>(full_bar(stage), phase, ctx, 3u)) {
-            alive = false;
+    if constexpr (kWarpWide) {
+      // ================= MMA issuer(s) (leader CTA only) =================
+      // Issuer `me` of MMAS takes the K slabs with (slab index in the tile) % MMAS == me and accumulates them
+      // in its own tensor-memory columns.
+      const int me = warp == kWarpMma ? 0 : 1;
+      if (leader) {
+        uint32_t acc_phase = 0;
+        bool alive = true;
+        int slab0 = 0;  // slabs of the tiles this CTA has finished: the ring position of the tile's first slab
+        const bool mprof = prof && me == 0;
+        long long t_full = 0, t_acc = 0, t_issue = 0, t_begin = mprof ? clock64() : 0;
+        const uint64_t ns_begin = mprof ? globaltimer_ns() : 0;
+        const uint32_t acc_tmem = tmem_base + static_cast<uint32_t>(me * BN);
+        for (int t = unit; t < num_tiles && alive; t += num_units, slab0 += k_slabs) {
+          const long long a0 = mprof ? clock64() : 0;
+          if (!__all_sync(0xffffffffu,
+                          wait_or_abort<kClusterAcquireWaits && CG == 2>(tmem_empty_bar, acc_phase ^ 1u, ctx, 2u)))
             break;
-          }
-          const long long w1 = mprof ? clock64() : 0;
-          t_full += w1 - w0;
+          if (mprof) t_acc += clock64() - a0;
           tc_fence_after();
-          const uint32_t sbase = smem_base + stage * L::kStageBytes;
-          const uint32_t sf_tmem = tmem_base + kAccCols + stage * L::kSfCols;
-          int next_stage = stage + MMAS;
-          uint32_t next_phase = phase;
-          if (next_stage >= STAGES) { next_stage -= STAGES; next_phase ^= 1u; }
-          const bool more = ks + MMAS < k_slabs;
-          // 64 fp4 values = 32 bytes = 2 descriptor address units inside the swizzled row: the helper steps the
-          // descriptors by 2, the scales of A by 4 columns and those of B by 4 per 128-row chunk per MMA.
-          // After the tile's last slab there is nothing to poll: it polls this slab's own, completed barrier.
-          const uint32_t ok = tc_slab_and_poll_next<CG>(
-              acc_tmem, operand_desc(sbase), operand_desc(sbase + L::kABytes), kIdesc, sf_tmem,
-              sf_tmem + 16 + sfb_half, 4 * L::kChunks, ks >= MMAS ? 1u : 0u, empty_bar(stage),
-              full_bar(more ? next_stage : stage), more ? next_phase : phase);
-          polled = more && ok != 0;
-          stage = next_stage;
-          phase = next_phase;
-          if (mprof) t_issue += clock64() - w1;
+          // A 64-wide tile uses half of a 128-row scale chunk of B: the MMA reads N / 32 scale columns from
+          // the address it is given, so the upper half starts two columns in.
+          uint32_t sfb_half = 0;
+          if constexpr (BN == 64) {
+            int tm, tn;
+            tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
+            sfb_half = static_cast<uint32_t>(tn & 1) * 2u;
+          }
+          // ring position of this issuer's first slab of the tile; from there it moves MMAS stages per slab
+          int stage = (slab0 + me) % STAGES;
+          uint32_t phase = static_cast<uint32_t>((slab0 + me) / STAGES) & 1u;
+          for (int ks = me; ks < k_slabs; ks += MMAS) {
+            const long long w0 = mprof ? clock64() : 0;
+            if (!__all_sync(0xffffffffu,
+                            wait_or_abort<kClusterAcquireWaits && CG == 2>(full_bar(stage), phase, ctx, 3u))) {
+              alive = false;
+              break;
+            }
+            const long long w1 = mprof ? clock64() : 0;
+            t_full += w1 - w0;
+            tc_fence_after();
+            const uint32_t sbase = smem_base + stage * L::kStageBytes;
+            const uint32_t sf_tmem = tmem_base + kAccCols + stage * L::kSfCols;
+            const uint64_t a_desc = operand_desc(sbase);
+            const uint64_t b_desc = operand_desc(sbase + L::kABytes);
+            if (elect_one()) {
+  #pragma unroll
+              for (int kb = 0; kb < 4; ++kb) {
+                // 64 fp4 values = 32 bytes = 2 descriptor address units inside the swizzled row
+                tc_mma<CG>(acc_tmem, a_desc + 2 * kb, b_desc + 2 * kb, kIdesc, sf_tmem + kb * 4,
+                           sf_tmem + 16 + kb * 4 * L::kChunks + sfb_half, (ks >= MMAS || kb) ? 1u : 0u);
+              }
+              if constexpr (CG == 2) tc_commit_pair(empty_bar(stage));
+              else tc_commit<CG>(empty_bar(stage));
+            }
+            __syncwarp();
+            if (mprof) t_issue += clock64() - w1;
+            stage += MMAS;
+            if (stage >= STAGES) { stage -= STAGES; phase ^= 1u; }
+          }
+          if (!alive) break;
+          if (elect_one()) {
+            if constexpr (CG == 2) tc_commit_pair(tmem_full_bar);
+            else tc_commit<CG>(tmem_full_bar);
+          }
+          __syncwarp();
+          acc_phase ^= 1u;
         }
-        if (!alive) break;
-        if constexpr (CG == 2) tc_commit_pair(tmem_full_bar);
-        else tc_commit<CG>(tmem_full_bar);
-        acc_phase ^= 1u;
+        if (mprof) {
+          counters[2] = t_full;
+          counters[3] = t_acc;
+          counters[4] = clock64() - t_begin;
+          counters[5] = t_issue;
+          counters[11] = globaltimer_ns() - ns_begin;
+        }
       }
-      if (mprof) {
-        counters[2] = t_full;
-        counters[3] = t_acc;
-        counters[4] = clock64() - t_begin;
-        counters[5] = t_issue;
-        counters[11] = globaltimer_ns() - ns_begin;
+    } else {
+      // ================= MMA issuer(s) (leader CTA only) =================
+      // Issuer `me` of MMAS takes the K slabs with (slab index in the tile) % MMAS == me and accumulates them
+      // in its own tensor-memory columns.
+      const int me = warp == kWarpMma ? 0 : 1;
+      if (leader && lane == 0) {
+        uint32_t acc_phase = 0;
+        bool alive = true;
+        int slab0 = 0;  // slabs of the tiles this CTA has finished: the ring position of the tile's first slab
+        const bool mprof = prof && me == 0;
+        long long t_full = 0, t_acc = 0, t_issue = 0, t_begin = mprof ? clock64() : 0;
+        const uint64_t ns_begin = mprof ? globaltimer_ns() : 0;
+        const uint32_t acc_tmem = tmem_base + static_cast<uint32_t>(me * BN);
+        for (int t = unit; t < num_tiles && alive; t += num_units, slab0 += k_slabs) {
+          const long long a0 = mprof ? clock64() : 0;
+          if (!wait_or_abort<kClusterAcquireWaits && CG == 2>(tmem_empty_bar, acc_phase ^ 1u, ctx, 2u)) break;
+          if (mprof) t_acc += clock64() - a0;
+          tc_fence_after();
+          // A 64-wide tile uses half of a 128-row scale chunk of B: the MMA reads N / 32 scale columns from
+          // the address it is given, so the upper half starts two columns in.
+          uint32_t sfb_half = 0;
+          if constexpr (BN == 64) {
+            int tm, tn;
+            tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
+            sfb_half = static_cast<uint32_t>(tn & 1) * 2u;
+          }
+          // ring position of this issuer's first slab of the tile; from there it moves MMAS stages per slab
+          int stage = (slab0 + me) % STAGES;
+          uint32_t phase = static_cast<uint32_t>((slab0 + me) / STAGES) & 1u;
+          bool polled = false;  // the poll issued with the previous slab already found this slab's barrier complete
+          for (int ks = me; ks < k_slabs; ks += MMAS) {
+            const long long w0 = mprof ? clock64() : 0;
+            if (!polled && !wait_or_abort<kClusterAcquireWaits && CG == 2>(full_bar(stage), phase, ctx, 3u)) {
+              alive = false;
+              break;
+            }
+            const long long w1 = mprof ? clock64() : 0;
+            t_full += w1 - w0;
+            tc_fence_after();
+            const uint32_t sbase = smem_base + stage * L::kStageBytes;
+            const uint32_t sf_tmem = tmem_base + kAccCols + stage * L::kSfCols;
+            int next_stage = stage + MMAS;
+            uint32_t next_phase = phase;
+            if (next_stage >= STAGES) { next_stage -= STAGES; next_phase ^= 1u; }
+            const bool more = ks + MMAS < k_slabs;
+            // 64 fp4 values = 32 bytes = 2 descriptor address units inside the swizzled row: the helper steps the
+            // descriptors by 2, the scales of A by 4 columns and those of B by 4 per 128-row chunk per MMA.
+            // After the tile's last slab there is nothing to poll: it polls this slab's own, completed barrier.
+            const uint32_t ok = tc_slab_and_poll_next<CG>(
+                acc_tmem, operand_desc(sbase), operand_desc(sbase + L::kABytes), kIdesc, sf_tmem,
+                sf_tmem + 16 + sfb_half, 4 * L::kChunks, ks >= MMAS ? 1u : 0u, empty_bar(stage),
+                full_bar(more ? next_stage : stage), more ? next_phase : phase);
+            polled = more && ok != 0;
+            stage = next_stage;
+            phase = next_phase;
+            if (mprof) t_issue += clock64() - w1;
+          }
+          if (!alive) break;
+          if constexpr (CG == 2) tc_commit_pair(tmem_full_bar);
+          else tc_commit<CG>(tmem_full_bar);
+          acc_phase ^= 1u;
+        }
+        if (mprof) {
+          counters[2] = t_full;
+          counters[3] = t_acc;
+          counters[4] = clock64() - t_begin;
+          counters[5] = t_issue;
+          counters[11] = globaltimer_ns() - ns_begin;
+        }
       }
     }
   } else if (warp < kWarpEpi0) {
@@ -680,25 +813,53 @@ __global__ void __launch_bounds__(kThreads + 32 * (MMAS - 1), 1)
       counters[10] = t_body;
     }
   } else if (warp == kWarpScaleProducer) {
-    // ================= TMA producer of the scale factors =================
-    // A thread of its own: issuing a TMA copy costs its thread on the order of a hundred cycles, and
-    // four of them in one thread per slab made that thread the slowest stage of the pipeline.
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool alive = true;
-      for (int t = unit; t < num_tiles && alive; t += num_units) {
-        int tm, tn;
-        tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
-        const int row_a = (tm * CG + static_cast<int>(rank)) * kBlockM;
-        const int k_first = (t % p.splits) * k_slabs;
-        for (int ks = k_first; ks < k_first + k_slabs; ++ks) {
-          if (!wait_or_abort(empty_bar(stage), phase ^ 1u, ctx, 1u)) { alive = false; break; }
-          const uint32_t sf_smem = smem_base + stage * L::kStageBytes + L::kABytes + L::kBBytes;
-          mbar_expect_tx(sfload_bar(stage), kScaleTx);
-          tma_load_3d<1>(sf_smem, &map_sfa, 0, ks * 4, row_a / 128, sfload_bar(stage));
-          tma_load_3d<1>(sf_smem + L::kSfaBytes, &map_sfb, 0, ks * 4, (tn * BN) / 128, sfload_bar(stage));
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+    if constexpr (kWarpWide) {
+      // ================= TMA producer of the scale factors =================
+      // A warp of its own: with the operand copies in the same issuing role that role was the slowest stage of
+      // the pipeline.
+      {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        for (int t = unit; t < num_tiles && alive; t += num_units) {
+          int tm, tn;
+          tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
+          const int row_a = (tm * CG + static_cast<int>(rank)) * kBlockM;
+          const int k_first = (t % p.splits) * k_slabs;
+          for (int ks = k_first; ks < k_first + k_slabs; ++ks) {
+            if (!__all_sync(0xffffffffu, wait_or_abort(empty_bar(stage), phase ^ 1u, ctx, 1u))) { alive = false; break; }
+            const uint32_t sf_smem = smem_base + stage * L::kStageBytes + L::kABytes + L::kBBytes;
+            if (elect_one()) {
+              mbar_expect_tx(sfload_bar(stage), kScaleTx);
+              tma_load_3d<1>(sf_smem, &map_sfa, 0, ks * 4, row_a / 128, sfload_bar(stage));
+              tma_load_3d<1>(sf_smem + L::kSfaBytes, &map_sfb, 0, ks * 4, (tn * BN) / 128, sfload_bar(stage));
+            }
+            __syncwarp();
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    } else {
+      // ================= TMA producer of the scale factors =================
+      // A thread of its own: issuing a TMA copy costs its thread on the order of a hundred cycles, and
+      // four of them in one thread per slab made that thread the slowest stage of the pipeline.
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        for (int t = unit; t < num_tiles && alive; t += num_units) {
+          int tm, tn;
+          tile_coords(t / p.splits, p.tiles_m, p.tiles_n, p.group_n, tm, tn);
+          const int row_a = (tm * CG + static_cast<int>(rank)) * kBlockM;
+          const int k_first = (t % p.splits) * k_slabs;
+          for (int ks = k_first; ks < k_first + k_slabs; ++ks) {
+            if (!wait_or_abort(empty_bar(stage), phase ^ 1u, ctx, 1u)) { alive = false; break; }
+            const uint32_t sf_smem = smem_base + stage * L::kStageBytes + L::kABytes + L::kBBytes;
+            mbar_expect_tx(sfload_bar(stage), kScaleTx);
+            tma_load_3d<1>(sf_smem, &map_sfa, 0, ks * 4, row_a / 128, sfload_bar(stage));
+            tma_load_3d<1>(sf_smem + L::kSfaBytes, &map_sfb, 0, ks * 4, (tn * BN) / 128, sfload_bar(stage));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
         }
       }
     }
